@@ -1,6 +1,6 @@
 """Device storage behind the cache manager's page numbers and state slots.
 
-One tensor per cache group, [calls in the group, pages, 2 (K, V), kv heads, page_size,
+One tensor per cache group, [calls in the group, pages, planes (K, V; or one shared row), kv heads, page_size,
 head_dim] in the engine's element type, so a (page, K|V, kv head) tile is one
 contiguous [page_size, head_dim] block; one [max_seqs, numel] array per mixer call
 that keeps per-request state, in the element type the mixer asked for.
@@ -19,7 +19,7 @@ def allocate_caches(groups: Sequence[CacheNeed], group_calls: Sequence[Sequence[
                     dtype: torch.dtype, device) -> List[torch.Tensor]:
     out = []
     for need, calls in zip(groups, group_calls):
-        out.append(torch.zeros((len(calls), num_pages, 2, need.n_kv_heads, page_size, need.head_dim), dtype=dtype,
+        out.append(torch.zeros((len(calls), num_pages, need.planes, need.n_kv_heads, page_size, need.head_dim), dtype=dtype,
                                device=device))
     return out
 
@@ -32,4 +32,4 @@ def allocate_states(needs: Dict, max_seqs: int, device) -> Dict:
 
 def cache_bytes_per_token(groups: Sequence[CacheNeed], group_calls: Sequence[Sequence[int]], dtype: torch.dtype) -> int:
     es = element_type(dtype).itemsize
-    return sum(2 * n.n_kv_heads * n.head_dim * es * len(c) for n, c in zip(groups, group_calls))
+    return sum(n.planes * n.n_kv_heads * n.head_dim * es * len(c) for n, c in zip(groups, group_calls))

@@ -48,18 +48,20 @@ def registered_architectures():
 
 
 def resolve_architecture(config: Mapping[str, Any], where: str = "config.json") -> Architecture:
-    """The architecture a config.json names: ``architectures[0]`` first, then ``model_type``."""
+    """The architecture a config.json names: ``architectures[0]`` first, then ``architecture``, then ``model_type``."""
     tried = []
     archs = config.get("architectures")
     if isinstance(archs, (list, tuple)):
         tried += [str(a) for a in archs]
+    if isinstance(config.get("architecture"), str):
+        tried.append(config["architecture"])
     if config.get("model_type") is not None:
         tried.append(str(config["model_type"]))
     for n in tried:
         if n in _ARCHS:
             return _ARCHS[n]
     if not tried:
-        raise ConfigError(f"{where}: neither 'architectures' nor 'model_type' names an architecture "
+        raise ConfigError(f"{where}: neither 'architectures' nor 'architecture' nor 'model_type' names an architecture "
                           f"(registered: {', '.join(registered_architectures())})")
     raise ConfigError(f"{where}: unsupported architecture {', '.join(repr(t) for t in tried)} "
                       f"(registered: {', '.join(registered_architectures())})")

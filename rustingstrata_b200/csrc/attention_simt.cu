@@ -29,7 +29,8 @@ constexpr int ROWS = WARPS * RPW;
 struct AttnParams {
     const void* q; long q_stride;          // [tokens, q_stride], head h at h*hd
     void* out; long out_stride;            // [tokens, out_stride]
-    const void* cache; long page_stride;   // [pages][2][n_kv][page_size][hd]
+    const void* cache; long page_stride;   // [pages][2][n_kv][page_size][hd]; or one plane whose rows are key and value at once
+    long v_offset;                         // elements from a key row to its value row: n_kv * page_size * hd, or 0 for one plane
     int num_pages, page_size;
     const int* block_table; int table_stride;
     const int* q_start;                    // [n_seqs + 1] first token row of each sequence in this step
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(const AttnP
                     const T* base = cache + (size_t)page * p.page_stride +
                                     ((size_t)kvh * p.page_size + (kpos % p.page_size)) * hd + d;
                     kv = to_f32<T>(base[0]);
-                    vv = to_f32<T>(base[(size_t)p.n_kv * p.page_size * hd]);
+                    vv = to_f32<T>(base[p.v_offset]);
                 } else if (d == 0) {
                     atomicOr(p.status, RS_STATUS_BAD_PAGE);
                 }
@@ -260,7 +261,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
                                 int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
                                 int n_q, int n_kv, int hd, int window, float scale, int decode, int split_keys,
                                 int max_splits, const int* split_start, float* partial, int partial_slots,
-                                const float* slopes, int* status, void* stream) {
+                                const float* slopes, int one_plane, int* status, void* stream) {
     if (n_work <= 0) return 0;
     if (hd % 16 || hd > 256 || hd <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
     if (decode && (split_keys % KT || split_keys <= 0 || max_splits <= 0 || partial == nullptr || partial_slots <= 0 ||
@@ -277,6 +278,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
     p.window = window; p.scale = scale; p.decode = decode; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
     p.slopes = slopes;
+    p.v_offset = one_plane ? 0 : (long)n_kv * page_size * hd;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RS_F32) return dispatch_hd<float, true>(p, n_work, s);
     if (dt == RS_BF16) return dispatch_hd<__nv_bfloat16, false>(p, n_work, s);
@@ -364,6 +366,7 @@ RS_EXPORT int rs_attention_decode_noalloc(const void* q, long q_stride, void* ou
     p.q_per_cta = 1;
     p.window = window; p.scale = scale; p.decode = 1; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.status = status; p.slopes = nullptr;
+    p.v_offset = (long)n_kv * page_size * hd;
     // what the array really holds for this shape, not what the caller said it would use: a split list that
     // disagrees with total_splits is flagged by the kernels (RS_STATUS_BAD_PLAN) instead of written past the array
     p.partial_slots = (int)((long)RS_NOALLOC_MAX_FLOATS / ((long)n_q * (hd + 2)));

@@ -123,6 +123,12 @@ class ModelRunner:
             table = torch.from_numpy(normal_table().copy()).to(device)
             out = {}
             for name, need in needs.items():
+                if need.optional:
+                    continue
+                if need.role == "choice_table":
+                    from ..weights.random_init import draw_values
+                    out[name] = torch.from_numpy(draw_values(seed, name, need, std, norm_std).reshape(need.shape)).to(device)
+                    continue
                 if need.role == "int_table":
                     t = torch.empty(need.shape, dtype=torch.int32, device=device)
                     ops.fill_random(t, tensor_key(seed, name), None, 0.0, 0.0)
@@ -163,8 +169,8 @@ class ModelRunner:
             self._meta_event.synchronize()      # the previous upload has left the pinned buffer
         return self._meta_host, self._meta_dev
 
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None, post=None
-             ) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None, post=None,
+             on_layer=None) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [wanted, vocab] on the device, in the order of the
         entries and of each entry's ``want`` (None when nothing is wanted).  Unknown requests are admitted.
         On an error nothing advances: pages taken for the step are given back.
@@ -178,7 +184,10 @@ class ModelRunner:
         A step of single tokens only is captured in a CUDA graph the first time its shape occurs (number of
         requests and logit rows, block-table width and attention splits rounded up to buckets) and replayed
         afterwards: the per-step index arrays live at fixed places of one device buffer that is refreshed
-        before every replay."""
+        before every replay.
+
+        ``on_layer(index, stream)`` is called after every entry of the run order with the float32 residual stream of
+        the step's tokens (a view that the next layer overwrites); such a step runs eagerly."""
         eng = self.engine
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -242,9 +251,10 @@ class ModelRunner:
         if device_tokens is not None and (device_tokens.dtype != torch.int32 or device_tokens.numel() < T
                                           or not device_tokens.is_cuda):
             raise StepError("device_tokens must be int32 on the device with one id per token")
-        graphable = self.use_graphs and self.model.capturable and bool((q_lens == 1).all())
+        graphable = self.use_graphs and self.model.capturable and bool((q_lens == 1).all()) and on_layer is None
         try:
             ctx, layout = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R, graphable)
+            ctx.on_layer = on_layer
 
             chain = (ops.CHAIN_DECODE and self.dtype == torch.bfloat16 and T <= ops.chain_max_rows()
                      and self.model.chain_safe)

@@ -99,14 +99,38 @@ def core():
                                        c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_simt.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                          c_void_p]
+                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                          c_void_p, c_void_p]
         lib.rs_attention_simt_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_simt_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_simt_partial_floats.restype = c_long
         lib.rs_fill_random.argtypes = [c_void_p, c_int, c_long, ctypes.c_ulonglong, c_long, c_void_p, c_float, c_float,
                                        c_void_p]
         lib.rs_sample.argtypes = [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        lib.rs_rmsnorm_add.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_float, c_void_p, c_int,
+                                       c_int, c_float, c_void_p, c_int, c_long, c_int, c_int, c_void_p]
+        lib.rs_concat_embed.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                        c_long, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_short_conv.argtypes = [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                      c_int, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_int, c_int, c_void_p]
+        lib.rs_block_linear.argtypes = [c_void_p, c_int, c_long, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                        c_long, c_long, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rs_gated_linear_recurrence.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_int,
+                                                   c_void_p, c_int, c_void_p, c_int, c_long, c_void_p, c_long, c_void_p,
+                                                   c_void_p, c_int, c_int, c_float, c_void_p]
+        lib.rs_latent_kv_write.argtypes = [c_void_p, c_long, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_int, c_int,
+                                           c_void_p, c_int, c_long, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_int, c_int, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int,
+                                           c_int, c_int, c_void_p, c_void_p]
+        lib.rs_relu_squared.argtypes = [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_void_p]
+        lib.rs_moe_route.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_void_p]
+        lib.rs_grouped_linear_rows_per_tile.argtypes = [c_int]
+        lib.rs_grouped_linear.argtypes = [c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_int, c_float, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
+                                       c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_void_p]
         _core = lib
     return _core
 
@@ -689,8 +713,11 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
                    head_dim: int, page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor,
                    split_keys: int = 128, max_splits: int = 1, split_start: Optional[torch.Tensor] = None,
                    total_splits: int = 0, partial: Optional[torch.Tensor] = None,
-                   slopes: Optional[torch.Tensor] = None) -> None:
+                   slopes: Optional[torch.Tensor] = None, one_plane: bool = False) -> None:
     """Paged causal attention (see csrc/attention_simt.cu).  q/out: [T, >= n_q*head_dim] views.
+
+    ``one_plane``: the cache is [pages, 1, n_kv, page_size, head_dim] and a row is key and value at once (a latent
+    shared by both); else [pages, 2, ...] with keys in plane 0 and values in plane 1.
 
     ``slopes``: float32 [n_q] or None: slopes[h] * (key position - query position) is added to every scaled score of
     head h (a position encoding that biases scores by distance instead of rotating q and k).
@@ -705,8 +732,9 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     _rows_contiguous(out, "out")
     if q.dtype != cache.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and cache must share an element type")
-    if tuple(cache.shape[1:]) != (2, n_kv, page_size, head_dim) or not cache.is_contiguous():
-        raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [pages, 2, {n_kv}, {page_size}, {head_dim}]")
+    planes = 1 if one_plane else 2
+    if tuple(cache.shape[1:]) != (planes, n_kv, page_size, head_dim) or not cache.is_contiguous():
+        raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [pages, {planes}, {n_kv}, {page_size}, {head_dim}]")
     if head_dim % 16 or head_dim > 256:
         raise KernelError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
     if n_q % n_kv:
@@ -725,7 +753,7 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q), _ptr(cache), cache.stride(0), cache.shape[0],
         page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q,
         n_kv, head_dim, int(window), float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start),
-        _ptr(partial), slots, _ptr(slopes),
+        _ptr(partial), slots, _ptr(slopes), 1 if one_plane else 0,
         _ptr(status), _stream()), "attention_simt", 2 if decode else 1)
 
 
@@ -773,16 +801,17 @@ def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_di
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                       head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor,
-                      force: str = "", slopes: Optional[torch.Tensor] = None) -> None:
+                      force: str = "", slopes: Optional[torch.Tensor] = None, one_plane: bool = False) -> None:
     """Attention of prompt portions; ``work`` lists (sequence, first query) tiles of ``attention_prefill_q_per_cta``
     tokens.  tcgen05 kernel (csrc/attention_prefill_tc.cu), mma.sync kernel (csrc/attention_prefill_mma.cu) or
     CUDA cores, whichever takes the shape; ``force`` names one.  Score biases (``slopes``) are the CUDA-core kernel's."""
     kind = attention_prefill_kernel(q.dtype, n_q, n_kv, head_dim, page_size, force)
-    if slopes is not None and kind != "simt":
-        raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score biases")
+    if (slopes is not None or one_plane) and kind != "simt":
+        raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score biases or reads a "
+                          "one-plane cache")
     if kind == "simt":
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
-                       scale, False, status, slopes=slopes)
+                       scale, False, status, slopes=slopes, one_plane=one_plane)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status)
     _rows_contiguous(q, "q")
@@ -825,15 +854,16 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor, split_keys: int,
                      max_splits: int, split_start: torch.Tensor, total_splits: int, partial: torch.Tensor,
                      force_simt: bool = False, slopes: Optional[torch.Tensor] = None,
-                     items: Optional[torch.Tensor] = None) -> None:
+                     items: Optional[torch.Tensor] = None, one_plane: bool = False) -> None:
     """Attention of sequences with one query token each: the tensor-core kernel (csrc/attention_decode_mma.cu)
     where it takes the shape, else the CUDA-core kernel's split form (always, when score biases are given).  Same
     partial-workspace layout.  ``items``: the step's list of live (sequence, kv head, split) items from
     :func:`attention_decode_items`, which a caller with several layers builds once per step; built here if not given."""
-    if force_simt or slopes is not None or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size):
+    if (force_simt or slopes is not None or one_plane
+            or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size)):
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
-                       total_splits=total_splits, partial=partial, slopes=slopes)
+                       total_splits=total_splits, partial=partial, slopes=slopes, one_plane=one_plane)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
     _rows_contiguous(q, "q")
@@ -896,3 +926,250 @@ def sample(logits: torch.Tensor, n_rows: int, out: torch.Tensor, status: torch.T
         raise KernelError("sample: temps and uniforms must both be float32")
     _check(core().rs_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(temps), _ptr(uniforms),
                             _ptr(out), _ptr(status), _stream()), "sample")
+
+
+# ----------------------------------------------------------------------------- parts with state, sandwich norms, experts
+def _any_code(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else dtype_code(t)
+
+
+def rmsnorm_add(x: torch.Tensor, delta: torch.Tensor, gain: torch.Tensor, eps: float, n_rows: int,
+                then_weight: Optional[torch.Tensor] = None, then_eps: float = 0.0,
+                out: Optional[torch.Tensor] = None) -> None:
+    """x[r] += delta[r] * rsqrt(mean(delta[r]^2) + eps) * gain  (gain: one number or [n]); with ``out``, also
+    out[r] = x[r] * rsqrt(mean(x[r]^2) + then_eps) * then_weight, the norm of the stream's next reader, in the same
+    kernel.  x and delta float32 [*, n]."""
+    _cuda(x, delta, gain, then_weight, out)
+    _rows_contiguous(x, "rmsnorm_add x")
+    _rows_contiguous(delta, "rmsnorm_add delta")
+    n = x.shape[1]
+    if x.dtype != torch.float32 or delta.dtype != torch.float32 or delta.shape[1] != n:
+        raise KernelError("rmsnorm_add: the stream and the sublayer's output are float32 of one width")
+    if gain.numel() not in (1, n) or not gain.is_contiguous():
+        raise KernelError(f"rmsnorm_add: gain holds {gain.numel()} values, neither 1 nor {n}")
+    if n_rows > min(x.shape[0], delta.shape[0]):
+        raise KernelError("rmsnorm_add: more rows than the buffers hold")
+    if out is not None:
+        _rows_contiguous(out, "rmsnorm_add out")
+        if then_weight is None or then_weight.numel() not in (1, n) or not then_weight.is_contiguous() or out.shape[1] != n \
+                or n_rows > out.shape[0]:
+            raise KernelError("rmsnorm_add: the following norm needs a weight of 1 or n values and an output of n columns")
+    _check(core().rs_rmsnorm_add(_ptr(x), x.stride(0), _ptr(delta), delta.stride(0), _ptr(gain), dtype_code(gain),
+                                 gain.numel(), float(eps), _ptr(then_weight if out is not None else None),
+                                 _any_code(then_weight), 0 if then_weight is None else then_weight.numel(), float(then_eps),
+                                 _ptr(out), _any_code(out), 0 if out is None else out.stride(0), n_rows, n, _stream()),
+           "rmsnorm_add")
+
+
+def concat_embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, row: Optional[torch.Tensor], cat: torch.Tensor,
+                 n_tokens: int, status: torch.Tensor) -> None:
+    """cat[t] = [x[t] | table[ids[t]]] in cat's element type, then x[t] = row (zeros when row is None)."""
+    _cuda(x, table, ids, row, cat, status)
+    _rows_contiguous(x, "concat_embed x")
+    _rows_contiguous(cat, "concat_embed cat")
+    n = x.shape[1]
+    if x.dtype != torch.float32 or ids.dtype != torch.int32 or table.shape[1] != n or cat.shape[1] != 2 * n \
+            or not table.is_contiguous() or n_tokens > min(x.shape[0], cat.shape[0], ids.numel()):
+        raise KernelError("concat_embed: x float32 [T, n], table [V, n], cat [T, 2n], ids int32 [T]")
+    if row is not None and (row.numel() != n or not row.is_contiguous()):
+        raise KernelError("concat_embed: row must hold n values")
+    _check(core().rs_concat_embed(_ptr(x), x.stride(0), _ptr(table), dtype_code(table), _ptr(ids), table.shape[0], _ptr(row),
+                                  _any_code(row), _ptr(cat), dtype_code(cat), cat.stride(0), n_tokens, n, _ptr(status),
+                                  _stream()), "concat_embed")
+
+
+def short_conv(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, state: torch.Tensor, seq_of_token: torch.Tensor,
+               q_start: torch.Tensor, slots: torch.Tensor, n_tokens: int, n_seqs: int, in_bias: Optional[torch.Tensor] = None,
+               bias: Optional[torch.Tensor] = None, add_input: bool = False) -> None:
+    """Causal convolution over time on each channel for the step's packed sequences (csrc/sequence_parts.cu).
+
+    x [T, C]; weight [C, taps] (the last column multiplies the current token); out [T, C], not x itself;
+    state: float32 [slots, >= (taps - 1) * C] view whose rows hold each request's last taps - 1 inputs (updated)."""
+    _cuda(x, weight, out, state, seq_of_token, q_start, slots, in_bias, bias)
+    _rows_contiguous(x, "short_conv x")
+    _rows_contiguous(out, "short_conv out")
+    C, taps = weight.shape
+    if x.shape[1] < C or out.shape[1] < C or not weight.is_contiguous() or n_tokens > min(x.shape[0], out.shape[0]):
+        raise KernelError(f"short_conv: x {tuple(x.shape)} / out {tuple(out.shape)} do not fit {C} channels")
+    if x.data_ptr() == out.data_ptr():
+        raise KernelError("short_conv: out must not be x (later tokens read earlier inputs)")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < (taps - 1) * C:
+        raise KernelError("short_conv: state must be float32 [slots, >= (taps - 1) * channels]")
+    for name, t in (("seq_of_token", seq_of_token), ("q_start", q_start), ("slots", slots)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"short_conv: {name} must be int32")
+    for name, t in (("in_bias", in_bias), ("bias", bias)):
+        if t is not None and (t.numel() != C or not t.is_contiguous()):
+            raise KernelError(f"short_conv: {name} must hold one value per channel")
+    _check(core().rs_short_conv(_ptr(x), dtype_code(x), x.stride(0), _ptr(in_bias), _any_code(in_bias), _ptr(weight),
+                                dtype_code(weight), _ptr(bias), _any_code(bias), _ptr(out), dtype_code(out), out.stride(0),
+                                _ptr(state), state.stride(0), _ptr(seq_of_token), _ptr(q_start), _ptr(slots), C, taps,
+                                1 if add_input else 0, n_tokens, n_seqs, _stream()), "short_conv", 2 if taps > 1 else 1)
+
+
+def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, in_block_stride: int,
+                 out_block_stride: int, bias: Optional[torch.Tensor] = None) -> None:
+    """out[t, b * out_block_stride + o] = bias[b, o] + sum_i weight[b, o, i] * x[t, b * in_block_stride + i]: one small
+    matrix per block of channels (a block-diagonal product), float32 accumulation.  weight [B, O, I] contiguous."""
+    _cuda(x, weight, out, bias)
+    _rows_contiguous(x, "block_linear x")
+    _rows_contiguous(out, "block_linear out")
+    if weight.dim() != 3 or not weight.is_contiguous():
+        raise KernelError("block_linear: weight must be contiguous [blocks, out, in]")
+    B, O, I = weight.shape
+    if (B - 1) * in_block_stride + I > x.shape[1] or (B - 1) * out_block_stride + O > out.shape[1] \
+            or n_rows > min(x.shape[0], out.shape[0]):
+        raise KernelError(f"block_linear: x {tuple(x.shape)} -> out {tuple(out.shape)} does not hold {B} blocks of "
+                          f"{I} -> {O} at strides {in_block_stride}, {out_block_stride}")
+    if bias is not None and (bias.numel() != B * O or not bias.is_contiguous()):
+        raise KernelError("block_linear: bias must hold blocks * out values")
+    _check(core().rs_block_linear(_ptr(x), dtype_code(x), x.stride(0), in_block_stride, _ptr(weight), dtype_code(weight),
+                                  _ptr(bias), _any_code(bias), _ptr(out), dtype_code(out), out.stride(0), out_block_stride,
+                                  n_rows, B, O, I, _stream()), "block_linear")
+
+
+def gated_linear_recurrence(gates: torch.Tensor, u: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor],
+                            lam: torch.Tensor, out: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+                            slots: torch.Tensor, n_seqs: int, decay: float) -> None:
+    """The real-gated linear recurrence of csrc/sequence_parts.cu over the step's packed sequences.
+
+    gates float32 [T, 2W] (pre-activations of the recurrence gate, then of the input gate), u float32 [T, W], y float32
+    [T, W] view (pre-activation of the GELU branch), lam [W]; out [T, W]; state float32 [slots, >= W] view (updated)."""
+    _cuda(gates, u, y, y_bias, lam, out, state, q_start, slots)
+    W = lam.numel()
+    for name, t in (("gates", gates), ("u", u), ("y", y)):
+        _rows_contiguous(t, "gated_linear_recurrence " + name)
+        if t.dtype != torch.float32:
+            raise KernelError(f"gated_linear_recurrence: {name} must be float32")
+    _rows_contiguous(out, "gated_linear_recurrence out")
+    if gates.shape[1] < 2 * W or u.shape[1] < W or y.shape[1] < W or out.shape[1] < W or not lam.is_contiguous():
+        raise KernelError("gated_linear_recurrence: buffers narrower than the recurrence")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < W:
+        raise KernelError("gated_linear_recurrence: state must be float32 [slots, >= width]")
+    if q_start.dtype != torch.int32 or slots.dtype != torch.int32:
+        raise KernelError("gated_linear_recurrence: q_start and slots must be int32")
+    if y_bias is not None and (y_bias.numel() != W or not y_bias.is_contiguous()):
+        raise KernelError("gated_linear_recurrence: y_bias must hold one value per channel")
+    _check(core().rs_gated_linear_recurrence(_ptr(gates), gates.stride(0), _ptr(u), u.stride(0), _ptr(y), y.stride(0),
+                                             _ptr(y_bias), _any_code(y_bias), _ptr(lam), dtype_code(lam), _ptr(out),
+                                             dtype_code(out), out.stride(0), _ptr(state), state.stride(0), _ptr(q_start),
+                                             _ptr(slots), W, n_seqs, float(decay), _stream()), "gated_linear_recurrence")
+
+
+def latent_kv_write(dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, q: torch.Tensor, q_head: int, q_nope: int,
+                    q_lat: torch.Tensor, cos_sin: Optional[torch.Tensor], n_rot: int, positions: torch.Tensor,
+                    seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, cache: Optional[torch.Tensor],
+                    rank: int, rot: int, lat: int, heads: int, n_tokens: int, status: torch.Tensor) -> None:
+    """Latent norm + interleaved rotation + write of [latent | rotated key part | 0...] into a one-plane cache
+    [pages, 1, 1, page_size, lat], and the rotated parts of the queries into q_lat[t, h * lat + rank : ...]."""
+    _cuda(dkv, norm_weight, q, q_lat, cos_sin, positions, seq_of_token, block_table, cache, status)
+    _rows_contiguous(dkv, "latent_kv_write dkv")
+    _rows_contiguous(q, "latent_kv_write q")
+    _rows_contiguous(q_lat, "latent_kv_write q_lat")
+    if dkv.dtype != torch.float32 or dkv.shape[1] < rank + rot or norm_weight.numel() != rank or not norm_weight.is_contiguous():
+        raise KernelError("latent_kv_write: dkv must be float32 [T, >= rank + rot] and the norm weight [rank]")
+    if q.shape[1] < heads * q_head or q_lat.shape[1] < heads * lat or q_nope + rot > q_head or rank + rot > lat:
+        raise KernelError("latent_kv_write: query buffers do not hold the heads")
+    if cache is not None and (tuple(cache.shape[1:]) != (1, 1, page_size, lat) or not cache.is_contiguous()):
+        raise KernelError(f"latent_kv_write: cache shape {tuple(cache.shape)} is not [pages, 1, 1, {page_size}, {lat}]")
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.shape[1] != n_rot or not cos_sin.is_contiguous()):
+        raise KernelError("latent_kv_write: cos_sin must be contiguous float32 [positions, n_rot]")
+    for name, t in (("positions", positions), ("seq_of_token", seq_of_token), ("block_table", block_table)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"latent_kv_write: {name} must be int32")
+    pos_stride = 1 if positions.dim() == 1 else positions.shape[1]
+    _check(core().rs_latent_kv_write(
+        _ptr(dkv), dkv.stride(0), _ptr(norm_weight), dtype_code(norm_weight), float(eps), _ptr(q), dtype_code(q), q.stride(0),
+        q_head, q_nope, _ptr(q_lat), dtype_code(q_lat), q_lat.stride(0), _ptr(cos_sin), n_rot if cos_sin is not None else 0,
+        0 if cos_sin is None else cos_sin.shape[0], _ptr(positions), pos_stride, _ptr(seq_of_token), _ptr(block_table),
+        block_table.stride(0), page_size, _ptr(cache), _any_code(cache), 0 if cache is None else cache.stride(0),
+        0 if cache is None else cache.shape[0], rank, rot, lat, heads, n_tokens, _ptr(status), _stream()), "latent_kv_write")
+
+
+def relu_squared(x: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    """out[r, c] = max(x[r, c], 0)^2 (same element type; in place allowed)."""
+    _cuda(x, out)
+    _rows_contiguous(x, "relu_squared x")
+    _rows_contiguous(out, "relu_squared out")
+    if x.dtype != out.dtype or x.shape[1] != out.shape[1] or n_rows > min(x.shape[0], out.shape[0]):
+        raise KernelError("relu_squared: x and out must share type and width")
+    _check(core().rs_relu_squared(_ptr(x), dtype_code(x), x.stride(0), _ptr(out), out.stride(0), n_rows, x.shape[1],
+                                  _stream()), "relu_squared")
+
+
+GROUPED_ROWS_SMALL, GROUPED_ROWS_TILED = 8, 64     # rows of one expert per CTA of the grouped product's two forms
+_GROUPED_ROWS_CHECKED = False
+
+
+def grouped_rows_per_tile(small: bool) -> int:
+    """Rows of one expert that a CTA of the grouped product takes (its row-streaming or its tiled form)."""
+    global _GROUPED_ROWS_CHECKED
+    if not _GROUPED_ROWS_CHECKED:
+        if (int(core().rs_grouped_linear_rows_per_tile(1)), int(core().rs_grouped_linear_rows_per_tile(0))) != \
+                (GROUPED_ROWS_SMALL, GROUPED_ROWS_TILED):
+            raise KernelError("grouped_linear: the compiled kernels' tile sizes differ from the launcher's")
+        _GROUPED_ROWS_CHECKED = True
+    return GROUPED_ROWS_SMALL if small else GROUPED_ROWS_TILED
+
+
+def moe_route(ids: torch.Tensor, table: torch.Tensor, n_experts: int, n_tokens: int, rows_per_tile: int,
+              order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor, status: torch.Tensor) -> None:
+    """Sorts the step's (token, k) pairs by the expert that ``table[ids[t], k]`` names: ``order`` [T * top] pair ids
+    grouped by expert, ``tiles`` [max_tiles, 3] (expert, first row in order, rows), ``n_tiles`` [1]."""
+    _cuda(ids, table, order, tiles, n_tiles, status)
+    V, top = table.shape
+    for name, t in (("ids", ids), ("table", table), ("order", order), ("tiles", tiles), ("n_tiles", n_tiles)):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"moe_route: {name} must be contiguous int32")
+    if order.numel() < n_tokens * top or ids.numel() < n_tokens:
+        raise KernelError("moe_route: order must hold tokens * top entries")
+    if rows_per_tile not in (grouped_rows_per_tile(True), grouped_rows_per_tile(False)):
+        raise KernelError("moe_route: rows_per_tile must be a tile size of the grouped product")
+    _check(core().rs_moe_route(_ptr(ids), _ptr(table), V, top, n_experts, n_tokens, rows_per_tile, _ptr(order), _ptr(tiles),
+                               _ptr(n_tiles), tiles.numel() // 3, _ptr(status), _stream()), "moe_route")
+
+
+def grouped_linear(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch.Tensor, order: torch.Tensor,
+                   tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, small: bool) -> None:
+    """One product per expert over the rows ``moe_route`` dealt to it.  Pair p reads row p // a_div of ``a`` and writes
+    row p of ``out``.  weight [E, N, K], or [E, 2N, K] when ``gated``: out = SiLU(a W[:N].T) * (a W[N:].T)."""
+    _cuda(a, weight, out, order, tiles, n_tiles)
+    _rows_contiguous(a, "grouped_linear a")
+    _rows_contiguous(out, "grouped_linear out")
+    if weight.dim() != 3 or not weight.is_contiguous():
+        raise KernelError("grouped_linear: weight must be contiguous [experts, rows, k]")
+    E, rows, K = weight.shape
+    N = rows // 2 if gated else rows
+    if a.shape[1] != K or out.shape[1] != N or (gated and rows % 2) or max_tiles * 3 > tiles.numel():
+        raise KernelError(f"grouped_linear: a {tuple(a.shape)} x weight {tuple(weight.shape)} -> out {tuple(out.shape)} "
+                          f"does not fit")
+    _check(core().rs_grouped_linear(_ptr(a), dtype_code(a), a.stride(0), a_div, _ptr(weight), dtype_code(weight),
+                                    weight.stride(0), _ptr(out), dtype_code(out), out.stride(0), _ptr(order), _ptr(tiles),
+                                    _ptr(n_tiles), max_tiles, N, K, 1 if gated else 0, 1 if small else 0, _stream()),
+           "grouped_linear")
+
+
+def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tensor, n_tokens: int,
+                shared: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None,
+                gate_weight: Optional[torch.Tensor] = None) -> None:
+    """out[t] = weight * sum_k pair_out[t * top + k] + sigmoid(h[t] . gate_weight) * shared[t]  (float32 out; the
+    second term only with ``shared``, its factor 1 without ``gate_weight``)."""
+    _cuda(pair_out, out, shared, h, gate_weight)
+    _rows_contiguous(pair_out, "moe_combine pair_out")
+    _rows_contiguous(out, "moe_combine out")
+    n = out.shape[1]
+    if pair_out.dtype != torch.float32 or out.dtype != torch.float32 or pair_out.shape[1] != n \
+            or pair_out.shape[0] < n_tokens * top or out.shape[0] < n_tokens:
+        raise KernelError("moe_combine: pair_out float32 [T * top, n], out float32 [T, n]")
+    if shared is not None:
+        _rows_contiguous(shared, "moe_combine shared")
+        if shared.shape[1] != n or shared.shape[0] < n_tokens:
+            raise KernelError("moe_combine: shared must be [T, n]")
+        if gate_weight is not None:
+            _rows_contiguous(h, "moe_combine h")
+            if gate_weight.numel() != n or not gate_weight.is_contiguous() or h.shape[1] != n:
+                raise KernelError("moe_combine: the gate reads h [T, n] with a weight of n values")
+    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), top, float(weight), _ptr(shared), _any_code(shared),
+                                 0 if shared is None else shared.stride(0), _ptr(h if gate_weight is not None else None),
+                                 _any_code(h), 0 if h is None else h.stride(0), _ptr(gate_weight), _any_code(gate_weight),
+                                 _ptr(out), out.stride(0), n_tokens, n, _stream()), "moe_combine")

@@ -172,6 +172,11 @@ class CausalLM:
             ctx.next_block_takes_owed = (k + 1 < len(self.calls)
                                          and self.blocks[self.calls[k + 1].layer].first_reader_takes_owed)
             self.blocks[info.layer].forward(residual, ctx, info)
+            if ctx.on_layer is not None:
+                if ctx.owed is not None:
+                    ctx.owed.finish()
+                    ctx.owed = None
+                ctx.on_layer(k, residual[: ctx.n_tokens])
         if ctx.owed is not None:
             ctx.owed.finish()
             ctx.owed = None

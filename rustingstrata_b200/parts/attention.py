@@ -45,6 +45,7 @@ class PagedAttention(Mixer):
     scale (float or None = 1/sqrt(head_dim)), kv_projection (bool, default True).
     tensors: q_proj, k_proj, v_proj, o_proj, and q_norm, k_norm when qk_norm."""
     chain_safe = True
+    one_plane = False      # a subclass whose cache row is key and value at once says True
 
     def __init__(self, spec, runtime, position=None):
         super().__init__(spec, runtime)
@@ -134,7 +135,7 @@ class PagedAttention(Mixer):
 
     def plan_key(self):
         if self.q_per_cta is None:
-            force = "simt" if self._score_slopes() is not None else ""
+            force = "simt" if self._score_slopes() is not None or self.one_plane else ""
             self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd,
                                                               self.runtime.page_size, force)
         return ("paged_attention", self.q_per_cta, self.window)
@@ -191,18 +192,28 @@ class PagedAttention(Mixer):
                             rot, pos.n_rot if rot is not None else 0,
                             ctx.positions, ctx.seq_of_token, table, rt.page_size, call.cache, write_kv, ctx.status,
                             stream=pos.stream if pos is not None else 0)
+        out = self._attend(qkv, ctx, call)
+        ctx.owed = ops.linear(out, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status,
+                              may_defer=ctx.may_owe and not ctx.store_output)
+
+    def _attend(self, q, ctx: StepContext, call: CallInfo):
+        """Attention of the step's queries ``q`` [T, >= heads * head size] over the call's cache: the portion form for
+        sequences with several tokens, the split form for single tokens.  Returns the [T, heads * head size] result."""
+        rt = self.runtime
+        table = ctx.block_tables[call.cache_group]
         out = rt.get_scratch("attn_out")[:, : self.q_width]
         plan = ctx.plans[self.plan_key()]
-        common = dict(q=qkv, out=out, cache=call.cache, block_table=table, q_start=ctx.q_start, kv_len=ctx.kv_len,
+        common = dict(q=q, out=out, cache=call.cache, block_table=table, q_start=ctx.q_start, kv_len=ctx.kv_len,
                       n_q=self.n_heads, n_kv=self.n_kv, head_dim=self.hd, page_size=rt.page_size, window=self.window,
-                      scale=self.scale, status=ctx.status)
+                      scale=self.scale, status=ctx.status, one_plane=self.one_plane)
         slopes = self._score_slopes()
+        simt = slopes is not None or self.one_plane
         if plan["n_prefill"]:
             ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes,
-                                  force="simt" if slopes is not None else "", **common)
+                                  force="simt" if simt else "", **common)
         if plan["n_decode"]:
             items = None
-            if slopes is None and ops.attention_decode_fast_ok(rt.dtype, self.n_heads, self.n_kv, self.hd, rt.page_size):
+            if not simt and ops.attention_decode_fast_ok(rt.dtype, self.n_heads, self.n_kv, self.hd, rt.page_size):
                 # built by the first layer of the step that needs it; the plan (and the list) is the step's, not the layer's
                 items = rt.get_scratch(self.items_name, torch.int32).view(-1)
                 if ("items", self.n_kv) not in plan:
@@ -212,4 +223,4 @@ class PagedAttention(Mixer):
                                  max_splits=plan["max_splits"], split_start=plan["split_start"],
                                  total_splits=plan["total_splits"], slopes=slopes, items=items,
                                  partial=rt.get_scratch("attn_partial", torch.float32), **common)
-        ctx.owed = ops.linear(out, self.w_o, residual, T, accumulate=True, status=ctx.status, may_defer=ctx.may_owe)
+        return out

@@ -136,6 +136,12 @@ class StepContext:
     may_owe: bool = False
     owed: Any = None
     next_block_takes_owed: bool = False
+    # A block that norms a sublayer's output before it joins the stream hands the mixer or feed-forward a buffer of
+    # its own in place of the stream and sets ``store_output``: the part then stores its output there instead of adding.
+    store_output: bool = False
+    # Called as on_layer(index in the run order, residual stream) after every entry of the run order, when set
+    # (tests and debugging read the stream layer by layer; a step that sets it is not captured).
+    on_layer: Any = None
 
 
 class Part:
@@ -202,6 +208,12 @@ class Norm(Part):
     takes_owed = False
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+    def forward_add(self, delta: torch.Tensor, x: torch.Tensor, n_rows: int, then: Optional["Norm"] = None,
+                    out: Optional[torch.Tensor] = None) -> None:
+        """x += norm(delta) for a float32 sublayer output ``delta``; with ``then`` and ``out`` also out = then(x), the
+        norm of the stream's next reader, fused when both norms can (else in turn)."""
         raise NotImplementedError
 
 

@@ -1,0 +1,149 @@
+"""Feed-forwards beyond the gated one: a plain two-matrix layer with a squared ReLU, and a mixture of experts whose
+choice is a table from token id to expert ids (no router to evaluate), with an optional shared expert.
+
+``table_moe``: every token uses the ``top`` experts its id names, each with weight 1 / top; an expert is
+down(SiLU(gate h) * (up h)) without biases.  A shared expert of the same form runs for every token and is added,
+multiplied by sigmoid(w_sg . h), one number per token.  The step's (token, k) pairs are sorted by expert on the device
+(nothing is read back, so a step can be captured), one grouped product per projection serves all experts, and a last
+kernel adds a token's pairs in ascending k together with the gated shared expert.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, StepContext
+from .registry import register_part
+from .spec import TensorNeed
+
+# rows of one expert that a CTA of the grouped product takes, in its row-streaming (True) and its tiled form; the
+# launcher checks them against the compiled kernels
+_ROWS_PER_TILE = {True: ops.GROUPED_ROWS_SMALL, False: ops.GROUPED_ROWS_TILED}
+
+
+@register_part("feed_forward", "relu2_mlp")
+class SquaredReluMLP(FeedForward):
+    """down(relu(up h)^2), no biases.  params: hidden, intermediate.  tensors: up_proj, down_proj."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec.params["hidden"])
+        self.inter = int(spec.params["intermediate"])
+        runtime.scratch("ff_act", runtime.max_batch_tokens, self.inter)
+
+    def tensor_needs(self):
+        t = self.spec.tensors
+        return {t["up_proj"]: TensorNeed((self.inter, self.hidden)), t["down_proj"]: TensorNeed((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        t = self.spec.tensors
+        self.w_up = tensors[t["up_proj"]].contiguous()
+        self.w_down = tensors[t["down_proj"]].contiguous()
+
+    def forward(self, h, residual, ctx: StepContext):
+        T = ctx.n_tokens
+        act = self.runtime.get_scratch("ff_act")[:, : self.inter]
+        ops.linear(h, self.w_up, act, T, status=ctx.status)
+        ops.relu_squared(act, act, T)
+        ops.linear(act, self.w_down, residual, T, accumulate=not ctx.store_output, status=ctx.status)
+
+
+@register_part("feed_forward", "table_moe")
+class TableMoE(FeedForward):
+    """params: hidden, vocab, experts, top, expert_ff, shared_ff (0 or None: no shared expert).
+    tensors: table [vocab, top]; expert_gate / expert_up / expert_down: name patterns with ``{e}`` for the expert's
+    number; shared_gate, shared_up, shared_down, shared_scale [1, hidden] when there is a shared expert."""
+    SMALL_PAIRS_PER_EXPERT = 4      # up to this many (token, k) pairs per expert on average the row-streaming form runs
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden, self.vocab = int(p["hidden"]), int(p["vocab"])
+        self.n_experts, self.top = int(p["experts"]), int(p["top"])
+        self.ff = int(p["expert_ff"])
+        self.shared_ff = int(p.get("shared_ff") or 0)
+        if not 1 <= self.top <= self.n_experts:
+            raise ValueError(f"table_moe: top {self.top} of {self.n_experts} experts")
+        rt = runtime
+        pairs = rt.max_batch_tokens * self.top
+        rt.scratch("moe_act", pairs, self.ff)
+        rt.scratch("moe_pair_out", pairs, self.hidden, torch.float32)
+        rt.scratch("moe_order", 1, pairs, torch.int32)
+        self.max_tiles_small = self._max_tiles(pairs, True)
+        rt.scratch("moe_tiles", 1, 3 * max(self.max_tiles_small, self._max_tiles(pairs, False)) + 4, torch.int32)
+        rt.scratch("moe_delta", rt.max_batch_tokens, self.hidden, torch.float32)
+        if self.shared_ff:
+            rt.scratch("moe_shared_act", rt.max_batch_tokens, self.shared_ff)
+            rt.scratch("moe_shared_gu", rt.max_batch_tokens, 2 * self.shared_ff)
+            rt.scratch("moe_shared_out", rt.max_batch_tokens, self.hidden, torch.float32)
+
+    def _max_tiles(self, pairs: int, small: bool) -> int:
+        """Row tiles the grouped product can meet: full tiles, plus at most one partly filled per expert in use."""
+        rows = _ROWS_PER_TILE[small]
+        return pairs // rows + min(self.n_experts, pairs)
+
+    def tensor_needs(self):
+        t = self.spec.tensors
+        needs = {t["table"]: TensorNeed((self.vocab, self.top), "choice_table", limit=self.n_experts)}
+        for e in range(self.n_experts):
+            needs[t["expert_gate"].format(e=e)] = TensorNeed((self.ff, self.hidden))
+            needs[t["expert_up"].format(e=e)] = TensorNeed((self.ff, self.hidden))
+            needs[t["expert_down"].format(e=e)] = TensorNeed((self.hidden, self.ff))
+        if self.shared_ff:
+            needs[t["shared_gate"]] = TensorNeed((self.shared_ff, self.hidden))
+            needs[t["shared_up"]] = TensorNeed((self.shared_ff, self.hidden))
+            needs[t["shared_down"]] = TensorNeed((self.hidden, self.shared_ff))
+            needs[t["shared_scale"]] = TensorNeed((1, self.hidden))
+        return needs
+
+    def load(self, tensors):
+        t, E = self.spec.tensors, self.n_experts
+        self.table = tensors[t["table"]].contiguous()
+        # all experts in one tensor each: [E, gate rows then up rows, hidden] and [E, hidden, ff]
+        self.w_gate_up = torch.stack([torch.cat([tensors[t["expert_gate"].format(e=e)], tensors[t["expert_up"].format(e=e)]],
+                                                dim=0) for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[t["expert_down"].format(e=e)] for e in range(E)]).contiguous()
+        if self.shared_ff:
+            g, u = tensors[t["shared_gate"]], tensors[t["shared_up"]]
+            self.shared_fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0)
+            if self.shared_fused:      # gate and up rows alternate: the product's epilogue applies SiLU(gate) * up
+                self.w_shared_gu = torch.stack([g, u], dim=1).reshape(2 * self.shared_ff, self.hidden).contiguous()
+            else:
+                self.w_shared_gu = torch.cat([g, u], dim=0).contiguous()
+            self.w_shared_down = tensors[t["shared_down"]].contiguous()
+            self.w_shared_scale = tensors[t["shared_scale"]].reshape(-1).contiguous()
+
+    def forward(self, h, residual, ctx: StepContext):
+        rt, T, top = self.runtime, ctx.n_tokens, self.top
+        pairs = T * top
+        small = pairs <= self.SMALL_PAIRS_PER_EXPERT * self.n_experts
+        max_tiles = self._max_tiles(pairs, small)
+        order = rt.get_scratch("moe_order", torch.int32).view(-1)
+        tiles = rt.get_scratch("moe_tiles", torch.int32).view(-1)
+        n_tiles, tiles = tiles[:1], tiles[4:]
+        act = rt.get_scratch("moe_act")[:, : self.ff]
+        pair_out = rt.get_scratch("moe_pair_out", torch.float32)[:, : self.hidden]
+        ops.moe_route(ctx.token_ids, self.table, self.n_experts, T, _ROWS_PER_TILE[small], order, tiles, n_tiles, ctx.status)
+        ops.grouped_linear(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True, small=small)
+        ops.grouped_linear(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, small=small)
+        shared_out = None
+        if self.shared_ff:
+            sact = rt.get_scratch("moe_shared_act")[:, : self.shared_ff]
+            shared_out = rt.get_scratch("moe_shared_out", torch.float32)[:, : self.hidden]
+            if self.shared_fused:
+                ops.linear_swiglu(h, self.w_shared_gu, sact, T, status=ctx.status)
+            else:
+                gu = rt.get_scratch("moe_shared_gu")[:, : 2 * self.shared_ff]
+                ops.linear(h, self.w_shared_gu, gu, T)
+                ops.silu_mul(gu, sact, T)
+            ops.linear(sact, self.w_shared_down, shared_out, T, status=ctx.status)
+        if ctx.store_output:
+            ops.moe_combine(pair_out, top, 1.0 / top, residual, T, shared=shared_out, h=h,
+                            gate_weight=self.w_shared_scale if self.shared_ff else None)
+        else:
+            delta = rt.get_scratch("moe_delta", torch.float32)[:, : self.hidden]
+            ops.moe_combine(pair_out, top, 1.0 / top, delta, T, shared=shared_out, h=h,
+                            gate_weight=self.w_shared_scale if self.shared_ff else None)
+            ops.residual_add(residual, delta, T)
+
+

@@ -62,4 +62,5 @@ class GatedMLP(FeedForward):
         else:
             ops.linear(h, self.w_gate_up, gate_up, T)
             ops.silu_mul(gate_up, act, T)
-        ctx.owed = ops.linear(act, self.w_down, residual, T, accumulate=True, status=ctx.status, may_defer=ctx.may_owe)
+        ctx.owed = ops.linear(act, self.w_down, residual, T, accumulate=not ctx.store_output, status=ctx.status,
+                              may_defer=ctx.may_owe and not ctx.store_output)

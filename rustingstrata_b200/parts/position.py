@@ -47,3 +47,34 @@ class NoPosition(PositionEncoding):
     chain_safe = True
     n_rot = 0
     cos_sin = None
+
+
+@register_part("position", "rope_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotation of neighbouring pairs (2i, 2i + 1), i < n_rot / 2, by position * base^(-2i / n_rot).
+
+    params: n_rot, base.  The table has the layout of the NEOX kind ([position, cos(n_rot/2) | sin(n_rot/2)], float64
+    angles rounded to float32); what differs is which coordinates a kernel pairs, which ``pairing`` tells.  It holds
+    as many positions as a request can reach: the model's limit, or what the cache pool holds if that is less."""
+    chain_safe = True
+    pairing = "interleaved"
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.n_rot = int(spec.params["n_rot"])
+        self.base = float(spec.params["base"])
+        if self.n_rot % 2:
+            raise ValueError(f"rope_interleaved: n_rot {self.n_rot} must be even")
+        self.rows = max(1, min(runtime.max_positions, runtime.pool_tokens))
+        self._key = ("rope_interleaved", self.n_rot, self.base, self.rows)
+
+    @property
+    def cos_sin(self) -> torch.Tensor:
+        return self.runtime.shared(self._key, self._table)
+
+    def _table(self) -> torch.Tensor:
+        half = self.n_rot // 2
+        inv = np.power(np.float64(self.base), -2.0 * np.arange(half, dtype=np.float64) / self.n_rot)
+        theta = np.arange(self.rows, dtype=np.float64)[:, None] * inv[None, :]
+        tab = np.concatenate([np.cos(theta), np.sin(theta)], axis=1).astype(np.float32)
+        return torch.from_numpy(tab).to(self.runtime.device)

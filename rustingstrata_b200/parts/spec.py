@@ -30,10 +30,14 @@ class TensorNeed:
 
     role: "matrix" (projection, drawn N(0, std) in random mode), "embedding"
     (token table, same distribution), "norm" (scale vector, ones or 1+N(0, s)),
-    "int_table" (integer table kept as int32).
+    "int_table" (integer table kept as int32), "choice_table" (integer table whose rows each hold
+    distinct values below ``limit``, e.g. the experts of a token).
+    ``optional``: the checkpoint may leave the tensor out; the part then finds it missing in ``load``.
     """
     shape: Tuple[int, ...]
     role: str = "matrix"
+    limit: int = 0
+    optional: bool = False
 
 
 @dataclass(frozen=True)
@@ -92,11 +96,14 @@ class CacheNeed:
 
     ``window`` None keeps every key; an integer keeps the most recent ``window`` keys
     (the current one included), so pages wholly older than that are given back.
+    ``planes``: 2 keeps a key row and a value row per token and head; 1 keeps one row that
+    serves as both (a latent from which keys and values are expanded).
     Calls with equal needs share a page pool ("cache group").
     """
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

@@ -53,7 +53,7 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     page = args.page_size
     pool_tokens = (args.max_tokens + page - 1) // page * page
-    eng = EngineConfig(dtype=args.dtype, page_size=page, num_pages=pool_tokens // page, max_seqs=8,
+    eng = EngineConfig(dtype=args.dtype, page_size=page, num_pages=pool_tokens // page, max_seqs=4,
                        max_batch_tokens=max(pool_tokens, 64), max_logit_rows=max(pool_tokens, 64))
     print(f"[trace_run] loading {args.model or args.random_config} ({args.dtype}, {pool_tokens // page} pages of "
           f"{page})", file=sys.stderr, flush=True)

@@ -43,6 +43,7 @@ class WeightsError(ValueError):
         super().__init__("\n".join(lines))
 
 
+INT_ROLES = ("int_table", "choice_table")
 _FLOAT_TAGS = ("BF16", "F16", "F32", "F64")
 _INT_TAGS = ("I64", "I32", "I16", "I8", "U8")
 
@@ -65,7 +66,7 @@ def match_names(manifest: Mapping[str, TensorNeed], entries: Mapping[str, Tensor
         elif _strip(want) in by_stripped and by_stripped[_strip(want)] not in used:
             pairs[want] = by_stripped[_strip(want)]
             used.add(by_stripped[_strip(want)])
-        else:
+        elif not manifest[want].optional:
             missing.append(want)
     unexpected = [n for n in entries if n not in used]
     return pairs, missing, unexpected
@@ -73,7 +74,7 @@ def match_names(manifest: Mapping[str, TensorNeed], entries: Mapping[str, Tensor
 
 def to_torch(arr: np.ndarray, tag: str, engine_dtype: torch.dtype, role: str) -> torch.Tensor:
     """One file tensor as a CPU torch tensor of the type the engine keeps it in."""
-    if role == "int_table":
+    if role in INT_ROLES:
         return torch.from_numpy(arr.astype(np.int32))
     if tag == "BF16":
         t = torch.from_numpy(arr.copy() if not arr.flags.writeable else arr).view(torch.bfloat16)
@@ -97,7 +98,7 @@ def load_checkpoint(model_dir: str, manifest: Mapping[str, TensorNeed], engine_d
         need, ent = manifest[want], entries[have]
         if tuple(need.shape) != tuple(ent.shape):
             wrong_shape.append((want, ent.shape, need.shape))
-        if need.role == "int_table":
+        if need.role in INT_ROLES:
             if ent.dtype not in _INT_TAGS:
                 wrong_type.append((want, f"file {ent.dtype}, model wants an integer table"))
         elif ent.dtype not in _FLOAT_TAGS:

@@ -101,6 +101,8 @@ def draw_values(seed: int, name: str, need: TensorNeed, std: float, norm_std: fl
     """Elements start .. start + count - 1 of the flattened tensor: float32, or int32 for an integer table."""
     n = int(np.prod(need.shape, dtype=np.int64)) if len(need.shape) else 1
     count = n - start if count < 0 else count
+    if need.role == "choice_table":
+        return draw_choices(seed, name, need)[start:start + count]
     z = draw_bits(tensor_key(seed, name), start, count)
     if need.role == "int_table":
         return (z & np.uint64(1)).astype(np.int32)
@@ -110,6 +112,22 @@ def draw_values(seed: int, name: str, need: TensorNeed, std: float, norm_std: fl
     v *= np.float32(scale)                                      # float32 multiply, then float32 add
     v += np.float32(shift)
     return v
+
+
+def draw_choices(seed: int, name: str, need: TensorNeed) -> np.ndarray:
+    """A table [rows, k] of distinct values below ``need.limit`` per row, flattened: the row's first value and a step
+    come from the tensor's stream, entry j is first + j * step modulo the limit (step small enough that the k values
+    do not wrap onto each other)."""
+    rows, k = need.shape
+    limit = int(need.limit)
+    if not 1 <= k <= limit:
+        raise ValueError(f"tensor '{name}': {k} distinct choices out of {limit}")
+    z = draw_bits(tensor_key(seed, name), 0, rows)
+    first = (z % np.uint64(limit)).astype(np.int64)
+    most = (limit - 1) // (k - 1) if k > 1 else 1
+    step = 1 + ((z >> np.uint64(32)) % np.uint64(most)).astype(np.int64)
+    table = (first[:, None] + step[:, None] * np.arange(k, dtype=np.int64)[None, :]) % limit
+    return table.astype(np.int32).reshape(-1)
 
 
 def draw_tensor(seed: int, name: str, need: TensorNeed, std: float, norm_std: float) -> Iterator[np.ndarray]:
@@ -135,13 +153,15 @@ def write_random_model(model_dir: str, config_dict: Mapping, manifest: Mapping[s
         json.dump(dict(config_dict), f, indent=2)
         f.write("\n")
     tag = "BF16" if store_dtype == "bfloat16" else "F32"
-    layout = [(name, "I32" if need.role == "int_table" else tag, tuple(need.shape)) for name, need in manifest.items()]
+    ints = ("int_table", "choice_table")
+    manifest = {name: need for name, need in manifest.items() if not need.optional}
+    layout = [(name, "I32" if need.role in ints else tag, tuple(need.shape)) for name, need in manifest.items()]
     w = SafetensorsWriter(os.path.join(model_dir, "model.safetensors"), layout,
                           metadata={"format": "pt", "seed": str(seed)})
     for i, (name, need) in enumerate(manifest.items()):
         parts = []
         for chunk in draw_tensor(seed, name, need, std, norm_std):
-            if need.role == "int_table":
+            if need.role in ints:
                 parts.append(chunk)
             elif tag == "BF16":
                 parts.append(f32_to_bf16_bits(chunk))
