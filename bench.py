@@ -95,7 +95,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run this many of the configuration's layers (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
-    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long"])
+    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex"])
+    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex: widths to run")
     ap.add_argument("--marginal", action="store_true", help="marginal cost of each kernel family inside the decode step")
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="with --marginal: tokens each request holds")
     ap.add_argument("--marginal-prefill", action="store_true",
@@ -118,6 +119,8 @@ def main() -> int:
         return mixed_workload(args)
     if args.workload == "32b-long":
         return long_context_workload(args)
+    if args.workload == "lokinex":
+        return lokinex_workload(args)
 
     import numpy as np
     import torch
@@ -353,6 +356,165 @@ def marginal_costs_prefill(args) -> int:
         key = "marginal_us_per_step" if label == "output head" else "marginal_us_per_layer"
         out[key][label] = per_step if label == "output head" else per_step / L
     out["ms_per_step_at_the_end"] = whole
+    print(json.dumps(out))
+    return 0
+
+
+def lokinex_config(width: int) -> dict:
+    """A Lokinex model whose layers resemble real ones at this width: latent attention with a 4:1 latent (rank width / 4,
+    heads of 64 + 64 query/key and 128 value coordinates), recurrent layers 5/4 of the width in blocks of 256, a dense
+    feed-forward of 4 x width, 32 experts of 3/4 width with 4 per token and a shared expert of twice that; four layers
+    (attention + dense, recurrence + experts, attention + experts, recurrence + experts) run twice by the loop."""
+    heads = width // 128
+    att = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": width // 4,
+                                                 "rot": {"base": 250000.0, "dims": 64}, "scale": 128 ** -0.5}}
+    rec = {"type": "rglru", "mixer": {"width": width * 5 // 4, "blocks": width * 5 // 4 // 256, "conv": 4}}
+    moe = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": width * 3 // 4}, "shared": {"ff": width * 3 // 2}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Lokinex", "vocab": 32768, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "layers": [dict(att, mlp=dense), dict(rec, mlp=moe), dict(att, mlp=moe), dict(rec, mlp=moe)],
+            "loop": {"start": 0, "stop": 4, "times": 2}}
+
+
+def qwen3_like(width: int) -> dict:
+    """The closest existing model at equal size: as many layer runs (8), the same width, vocabulary and head size, a gated
+    feed-forward with as many weights as the dense one above (3 matrices of 8/3 width against 2 of 4 width)."""
+    return dict(QWEN3_8B, vocab_size=32768, hidden_size=width, num_hidden_layers=8, num_attention_heads=width // 128,
+                num_key_value_heads=max(1, width // 512), head_dim=128, intermediate_size=width * 8 // 3 // 64 * 64,
+                max_position_embeddings=8192)
+
+
+class OpTimer:
+    """Device time per launcher of ``kernels.ops`` inside a region: CUDA events around every call of the listed
+    launchers (eager steps only), summed per name after a synchronisation."""
+    NAMES = ("embed", "rmsnorm", "rmsnorm_add", "concat_embed", "short_conv", "block_linear", "gated_linear_recurrence",
+             "gated_linear_recurrence_gates", "latent_kv_write", "relu_squared", "moe_route", "grouped_linear", "moe_combine",
+             "gather_rows", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
+             "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand")
+
+    def __init__(self):
+        self.events, self.real = [], {}
+
+    def __enter__(self):
+        import torch
+        from rustingstrata_b200.kernels import ops
+        for name in self.NAMES:
+            fn = getattr(ops, name, None)
+            if fn is None:
+                continue
+            self.real[name] = fn
+
+            def timed(*a, _fn=fn, _name=name, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = _fn(*a, **k)
+                e1.record()
+                self.events.append((_name, e0, e1))
+                return out
+            setattr(ops, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        from rustingstrata_b200.kernels import ops
+        for name, fn in self.real.items():
+            setattr(ops, name, fn)
+
+    def totals(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self.events:
+            t = out.setdefault(name, [0, 0.0])
+            t[0] += 1
+            t[1] += e0.elapsed_time(e1) * 1000
+        return {k: {"calls": v[0], "us": round(v[1], 1)} for k, v in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def lokinex_workload(args) -> int:
+    """Prefill of one 2,048-token prompt and decode at batch 8 (2,048 tokens held each) of the Lokinex design at layer
+    sizes that resemble a real model's, beside the Qwen3 dense decoder at equal width, depth and vocabulary; device time
+    per kernel family of one prompt step and one decode step of each (eager steps with events around every launcher)."""
+    import numpy as np
+    import torch
+    from rustingstrata_b200 import Engine
+    from rustingstrata_b200.engine import StepEntry, roofline
+    from rustingstrata_b200.sampling import SamplingParams
+    pk = roofline.peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+    clocks = ClockSampler()
+    clocks.start()
+    out = {"workload": "lokinex", "prompt_len": PROMPT, "batch": args.batch, "steps": args.steps, "dtype": "bf16",
+           "data": "synthetic", "weights": "random N(0,0.02) bf16", "peaks": pk["source"], "sizes": {}}
+    for width in [int(x) for x in args.sizes.split(",")]:
+        rec = {}
+        for name, cfg in (("lokinex", lokinex_config(width)), ("qwen3", qwen3_like(width))):
+            V = cfg.get("vocab", cfg.get("vocab_size"))
+            eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=args.batch * CONTEXT,
+                         max_batch_tokens=PROMPT, max_seqs=args.batch)
+            runner = eng.runner
+            rng = np.random.default_rng(0)
+
+            def finish_all():
+                eng.drain()
+                for r in list(eng.scheduler.running):
+                    eng.scheduler.running.remove(r)
+                    runner.release(r.rid)
+                    eng._samplers.pop(r.rid, None)
+
+            def prompt_ms():
+                eng.add_request(rng.integers(0, V, size=PROMPT).tolist(), CONTEXT - PROMPT, SamplingParams())
+                eng.lookahead = False
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                ev0.record()
+                eng.step()
+                ev1.record()
+                torch.cuda.synchronize()
+                eng.lookahead = True
+                finish_all()
+                return ev0.elapsed_time(ev1)
+            for _ in range(3):
+                prompt_ms()
+            pms = float(np.median([prompt_ms() for _ in range(5)]))
+            flops = roofline.step_flops(runner.model, [PROMPT], [PROMPT], 1)
+            for _ in range(args.batch):
+                eng.add_request(rng.integers(0, V, size=PROMPT).tolist(), CONTEXT - PROMPT, SamplingParams())
+            while eng.scheduler.waiting or any(r.prefilling for r in eng.scheduler.running):
+                eng.step()
+            for _ in range(args.warmup):
+                eng.step()
+            kv_tokens = sum(runner.length(r.rid) for r in eng.scheduler.running)
+            dms = eng.decode_steps_device_timed(args.steps, warmup=3)
+            launches = eng.kernels_in_timed_steps / args.steps
+            dec = roofline.decode_roofline(runner.model, runner.kv_bytes_per_token, kv_tokens, dms, pk)
+            # device time per launcher: one eager decode step of the same batch, one eager prompt step
+            eng.drain()
+            graphs, runner.use_graphs = runner.use_graphs, False
+            with OpTimer() as t_dec:
+                for _ in range(3):
+                    eng.step()
+                eng.drain()
+                t_dec.events.clear()
+                eng.step()
+                eng.drain()
+            dec_ops = t_dec.totals()
+            finish_all()
+            with OpTimer() as t_pre:
+                prompt_ms()
+                t_pre.events.clear()
+                prompt_ms()
+            pre_ops = t_pre.totals()
+            runner.use_graphs = graphs
+            rec[name] = {
+                "prefill_tok_s": PROMPT / pms * 1000, "prefill_ms": pms, "prefill_tflops": flops / pms / 1e9,
+                "prefill_frac_of_tensor_peak": flops / (pms / 1000) / (pk["bf16_tflops"] * 1e12),
+                "decode_tok_s": args.batch / dms * 1000, "decode_ms_per_step": dms, "decode_launches_per_step": launches,
+                "decode_gbs": dec["achieved"], "decode_frac_of_hbm_peak": dec["frac"],
+                "weight_mb": roofline.weight_bytes(runner.model) / 1e6, "kv_bytes_per_token": runner.kv_bytes_per_token,
+                "prefill_step_us_by_launcher": pre_ops, "decode_step_us_by_launcher": dec_ops}
+            del eng, runner
+            torch.cuda.empty_cache()
+        out["sizes"][str(width)] = rec
+    out["clocks"] = clocks.stop()
     print(json.dumps(out))
     return 0
 

@@ -1,5 +1,5 @@
 // Paged causal attention on CUDA cores, for any head size that is a multiple of 16 up
-// to 256, any number of heads and groups, float32 or bfloat16 cache: the attention of
+// to 576, any number of heads and groups, float32 or bfloat16 cache: the attention of
 // the 32-bit engine and the general fallback of the bfloat16 engine.
 //
 // Two launch forms share one kernel body:
@@ -240,7 +240,8 @@ int dispatch_hd(const AttnParams& p, int n_work, cudaStream_t s) {
     if (p.hd <= 32) return launch_attention<T, 1, PRECISE>(p, n_work, s);
     if (p.hd <= 64) return launch_attention<T, 2, PRECISE>(p, n_work, s);
     if (p.hd <= 128) return launch_attention<T, 4, PRECISE>(p, n_work, s);
-    return launch_attention<T, 8, PRECISE>(p, n_work, s);
+    if (p.hd <= 256) return launch_attention<T, 8, PRECISE>(p, n_work, s);
+    return launch_attention<T, 18, PRECISE>(p, n_work, s);       // up to 576: a 512-wide latent with a 64-wide rotated part
 }
 }  // namespace
 
@@ -263,7 +264,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
                                 int max_splits, const int* split_start, float* partial, int partial_slots,
                                 const float* slopes, int one_plane, int* status, void* stream) {
     if (n_work <= 0) return 0;
-    if (hd % 16 || hd > 256 || hd <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
+    if (hd % 16 || hd > 576 || hd <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
     if (decode && (split_keys % KT || split_keys <= 0 || max_splits <= 0 || partial == nullptr || partial_slots <= 0 ||
                    split_start == nullptr))
         return (int)cudaErrorInvalidValue;

@@ -82,8 +82,11 @@ struct GroupedParams {
     const void* w; int w_dt; long w_expert_stride;           // [E][rows][K], rows = N (plain) or 2N (gated)
     void* out; int out_dt; long out_stride;                  // [P, N]
     const int* order; const int* tiles; const int* n_tiles;
-    int N, K, gated;
+    int N, K, gated;          // gated: 0 plain; 1 gate rows [0, N) and up rows [N, 2N); 2 gate row 2n, up row 2n + 1
 };
+
+__device__ __forceinline__ size_t gate_row(const GroupedParams& p, int n) { return p.gated == 2 ? 2 * (size_t)n : (size_t)n; }
+__device__ __forceinline__ size_t up_row(const GroupedParams& p, int n) { return p.gated == 2 ? 2 * (size_t)n + 1 : (size_t)p.N + n; }
 
 __device__ __forceinline__ float silu_exact(float g) { return g / (1.0f + expf(-g)); }
 
@@ -114,8 +117,8 @@ __global__ void __launch_bounds__(256) grouped_linear_tile_kernel(const GroupedP
             const int pr = pair_of_row[r];
             As[kk][r] = (pr >= 0 && gk < p.K) ? load_any(p.a, p.a_dt, (size_t)(pr / p.a_div) * p.a_stride + gk) : 0.f;
             const bool ok = gn < p.N && gk < p.K;
-            Ws[kk][r] = ok ? load_any(p.w, p.w_dt, wb + (size_t)gn * p.K + gk) : 0.f;
-            if (p.gated) Us[kk][r] = ok ? load_any(p.w, p.w_dt, wb + (size_t)(p.N + gn) * p.K + gk) : 0.f;
+            Ws[kk][r] = ok ? load_any(p.w, p.w_dt, wb + gate_row(p, gn) * p.K + gk) : 0.f;
+            if (p.gated) Us[kk][r] = ok ? load_any(p.w, p.w_dt, wb + up_row(p, gn) * p.K + gk) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -168,6 +171,7 @@ __global__ void __launch_bounds__(256) grouped_linear_rows_kernel(const GroupedP
 #pragma unroll
         for (int r = 0; r < GR_ROWS; ++r) { acc[c][r] = 0.f; accu[c][r] = 0.f; }
     const size_t wb = (size_t)e * p.w_expert_stride;
+    const bool vec = p.w_dt == RS_BF16 && p.K % 8 == 0 && p.w_expert_stride % 8 == 0 && ((size_t)p.w & 15) == 0;
     for (int k0 = 0; k0 < p.K; k0 += GR_KC) {
         __syncthreads();
         const int kc = min(GR_KC, p.K - k0);
@@ -181,9 +185,33 @@ __global__ void __launch_bounds__(256) grouped_linear_rows_kernel(const GroupedP
         for (int c = 0; c < CPW; ++c) {
             const int gn = n0 + warp * CPW + c;
             if (gn >= p.N) continue;
+            const size_t wrow = wb + gate_row(p, gn) * p.K + k0, urow = wb + up_row(p, gn) * p.K + k0;
+            if (vec) {
+                // eight bfloat16 weights per lane and load (16 bytes), the rows' values from shared memory
+                const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(p.w);
+                for (int kk = lane * 8; kk < kc; kk += 256) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wp + wrow + kk);
+                    uint4 uv = make_uint4(0, 0, 0, 0);
+                    if (p.gated) uv = *reinterpret_cast<const uint4*>(wp + urow + kk);
+                    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+                    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float w0 = __low2float(w2[q]), w1 = __high2float(w2[q]);
+                        const float u0 = __low2float(u2[q]), u1 = __high2float(u2[q]);
+#pragma unroll
+                        for (int r = 0; r < GR_ROWS; ++r) {
+                            const float a0 = As[r][kk + 2 * q], a1 = As[r][kk + 2 * q + 1];
+                            acc[c][r] = fmaf(a1, w1, fmaf(a0, w0, acc[c][r]));
+                            if (p.gated) accu[c][r] = fmaf(a1, u1, fmaf(a0, u0, accu[c][r]));
+                        }
+                    }
+                }
+                continue;
+            }
             for (int kk = lane; kk < kc; kk += 32) {
-                const float w = load_any(p.w, p.w_dt, wb + (size_t)gn * p.K + k0 + kk);
-                const float u = p.gated ? load_any(p.w, p.w_dt, wb + (size_t)(p.N + gn) * p.K + k0 + kk) : 0.f;
+                const float w = load_any(p.w, p.w_dt, wrow + kk);
+                const float u = p.gated ? load_any(p.w, p.w_dt, urow + kk) : 0.f;
 #pragma unroll
                 for (int r = 0; r < GR_ROWS; ++r) {
                     acc[c][r] = fmaf(As[r][kk], w, acc[c][r]);
@@ -222,9 +250,32 @@ RS_EXPORT int rs_grouped_linear(const void* a, int a_dt, long a_stride, int a_di
     return rs_launch_result();
 }
 
-// out[t, :] = weight * sum_k pair_out[t * top + k, :] + sigmoid(h[t, :] . gate_w) * shared[t, :]
+// out[i, :] = src[idx[i] / div, :] (rows of n elements of `es` bytes)
+__global__ void gather_rows_kernel(const unsigned char* __restrict__ src, long src_stride_bytes, const int* __restrict__ idx,
+                                   int div, unsigned char* __restrict__ out, long out_stride_bytes, int row_bytes) {
+    const unsigned char* s = src + (size_t)(idx[blockIdx.x] / div) * src_stride_bytes;
+    unsigned char* o = out + (size_t)blockIdx.x * out_stride_bytes;
+    if (row_bytes % 16 == 0 && ((size_t)s & 15) == 0 && ((size_t)o & 15) == 0) {
+        for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(o)[i] = reinterpret_cast<const uint4*>(s)[i];
+    } else {
+        for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) o[i] = s[i];
+    }
+}
+
+RS_EXPORT int rs_gather_rows(const void* src, long src_stride_bytes, const int* idx, int div, void* out,
+                             long out_stride_bytes, int row_bytes, int n_rows, void* stream) {
+    if (n_rows <= 0) return 0;
+    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const unsigned char*)src, src_stride_bytes, idx, div,
+                                                                (unsigned char*)out, out_stride_bytes, row_bytes);
+    return rs_launch_result();
+}
+
+// out[t, :] = weight * sum_k pair_out[row(t * top + k), :] + sigmoid(h[t, :] . gate_w) * shared[t, :],
+// row(p) = pair_row ? pair_row[p] : p
 // (shared == null: no shared expert).  out is float32 [T, n].
-__global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair_stride, int top, float weight,
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair_stride, const int* __restrict__ pair_row,
+                                   int top, float weight,
                                    const void* __restrict__ shared, int shared_dt, long shared_stride,
                                    const void* __restrict__ h, int h_dt, long h_stride, const void* __restrict__ gate_w,
                                    int gate_dt, float* __restrict__ out, long out_stride, int n) {
@@ -242,18 +293,21 @@ __global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair
     }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < top; ++k) v += pair_out[(size_t)(t * top + k) * pair_stride + i];
+        for (int k = 0; k < top; ++k) {
+            const int pr = t * top + k;
+            v += pair_out[(size_t)(pair_row != nullptr ? pair_row[pr] : pr) * pair_stride + i];
+        }
         v *= weight;
         if (shared != nullptr) v = fmaf(gate, load_any(shared, shared_dt, (size_t)t * shared_stride + i), v);
         out[(size_t)t * out_stride + i] = v;
     }
 }
 
-RS_EXPORT int rs_moe_combine(const float* pair_out, long pair_stride, int top, float weight, const void* shared,
+RS_EXPORT int rs_moe_combine(const float* pair_out, long pair_stride, const int* pair_row, int top, float weight, const void* shared,
                              int shared_dt, long shared_stride, const void* h, int h_dt, long h_stride, const void* gate_w,
                              int gate_dt, float* out, long out_stride, int n_tokens, int n, void* stream) {
     if (n_tokens <= 0) return 0;
-    moe_combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(pair_out, pair_stride, top, weight, shared, shared_dt,
+    moe_combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(pair_out, pair_stride, pair_row, top, weight, shared, shared_dt,
                                                                   shared_stride, h, h_dt, h_stride, gate_w, gate_dt, out,
                                                                   out_stride, n);
     return rs_launch_result();

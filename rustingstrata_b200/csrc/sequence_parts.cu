@@ -283,6 +283,92 @@ __global__ void gated_linear_recurrence_kernel(const RecurrenceParams p) {
     *sp = S;
 }
 
+// The same recurrence for long portions, in three kernels.  The host cuts every sequence's tokens of the step into
+// chunks of at most RS_SCAN_CHUNK (chunk_seq[k], chunk_start[k]: sequence and first local token; the chunks of a
+// sequence are consecutive, seq_first_chunk[s] .. seq_first_chunk[s + 1]).  (1) a thread per (chunk, channel) runs the
+// chunk from S = 0 and leaves the chunk's map S_out = A S_in + B (A the product of its a_t); (2) a thread per
+// (sequence, channel) walks the sequence's chunks in order, leaves every chunk's S_in and the final S in the state;
+// (3) a thread per (chunk, channel) runs the chunk again from its S_in and writes the outputs.
+struct ScanChunks {
+    const int* chunk_seq; const int* chunk_start; const int* seq_first_chunk;
+    int n_chunks, chunk_len;
+    float* work;                                  // [3][n_chunks][W]: A, B, S_in
+};
+
+__device__ __forceinline__ void recurrence_terms(const RecurrenceParams& p, size_t t, int c, float k, float& a, float& b) {
+    const float r = sigmoid_f32(p.gates[t * p.gates_stride + c]);
+    const float ig = sigmoid_f32(p.gates[t * p.gates_stride + p.W + c]);
+    const float log_a = k * r;
+    a = expf(log_a);
+    b = sqrtf(-expm1f(2.0f * log_a)) * ig * p.u[t * p.u_stride + c];
+}
+
+template <int PHASE>
+__global__ void recurrence_chunk_kernel(const RecurrenceParams p, const ScanChunks sc) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)sc.n_chunks * p.W) return;
+    const int ch = (int)(idx / p.W), c = (int)(idx % p.W);
+    const int s = sc.chunk_seq[ch], l0 = sc.chunk_start[ch];
+    const int row0 = p.q_start[s], n = min(sc.chunk_len, p.q_start[s + 1] - row0 - l0);
+    const float k = -p.decay_c * softplus_f32(load_any(p.lam, p.lam_dt, c));
+    const size_t slot = (size_t)ch * p.W + c, plane = (size_t)sc.n_chunks * p.W;
+    if (PHASE == 1) {
+        float A = 1.f, B = 0.f;
+        for (int li = 0; li < n; ++li) {
+            float a, b;
+            recurrence_terms(p, (size_t)(row0 + l0 + li), c, k, a, b);
+            A *= a;
+            B = fmaf(a, B, b);
+        }
+        sc.work[slot] = A;
+        sc.work[plane + slot] = B;
+    } else {
+        float S = sc.work[2 * plane + slot];
+        const float yb = p.y_bias != nullptr ? load_any(p.y_bias, p.y_bias_dt, c) : 0.f;
+        for (int li = 0; li < n; ++li) {
+            const size_t t = (size_t)(row0 + l0 + li);
+            float a, b;
+            recurrence_terms(p, t, c, k, a, b);
+            S = fmaf(a, S, b);
+            store_any(p.out, p.out_dt, t * p.out_stride + c, S * gelu_tanh_f32(p.y[t * p.y_stride + c] + yb));
+        }
+    }
+}
+
+__global__ void recurrence_carry_kernel(const RecurrenceParams p, const ScanChunks sc) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)p.n_seqs * p.W) return;
+    const int s = (int)(idx / p.W), c = (int)(idx % p.W);
+    float* sp = p.state + (size_t)p.slots[s] * p.state_stride + c;
+    float S = *sp;
+    const size_t plane = (size_t)sc.n_chunks * p.W;
+    for (int ch = sc.seq_first_chunk[s]; ch < sc.seq_first_chunk[s + 1]; ++ch) {
+        const size_t slot = (size_t)ch * p.W + c;
+        sc.work[2 * plane + slot] = S;
+        S = fmaf(sc.work[slot], S, sc.work[plane + slot]);
+    }
+    *sp = S;
+}
+
+RS_EXPORT int rs_gated_linear_recurrence_chunked(const float* gates, long gates_stride, const float* u, long u_stride,
+                                                 const float* y, long y_stride, const void* y_bias, int y_bias_dt,
+                                                 const void* lam, int lam_dt, void* out, int out_dt, long out_stride,
+                                                 float* state, long state_stride, const int* q_start, const int* slots,
+                                                 int W, int n_seqs, float decay_c, const int* chunk_seq,
+                                                 const int* chunk_start, const int* seq_first_chunk, int n_chunks,
+                                                 int chunk_len, float* work, void* stream) {
+    if (n_seqs <= 0 || W <= 0 || n_chunks <= 0) return 0;
+    RecurrenceParams p{gates, gates_stride, u, u_stride, y, y_stride, y_bias, y_bias_dt, lam, lam_dt, out, out_dt,
+                       out_stride, state, state_stride, q_start, slots, W, n_seqs, decay_c};
+    ScanChunks sc{chunk_seq, chunk_start, seq_first_chunk, n_chunks, chunk_len, work};
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned gc = (unsigned)(((long)n_chunks * W + 127) / 128), gs = (unsigned)(((long)n_seqs * W + 127) / 128);
+    recurrence_chunk_kernel<1><<<gc, 128, 0, s>>>(p, sc);
+    recurrence_carry_kernel<<<gs, 128, 0, s>>>(p, sc);
+    recurrence_chunk_kernel<2><<<gc, 128, 0, s>>>(p, sc);
+    return rs_launch_result();
+}
+
 RS_EXPORT int rs_gated_linear_recurrence(const float* gates, long gates_stride, const float* u, long u_stride, const float* y,
                                          long y_stride, const void* y_bias, int y_bias_dt, const void* lam, int lam_dt,
                                          void* out, int out_dt, long out_stride, float* state, long state_stride,

@@ -69,8 +69,9 @@ def flops_per_token(model) -> float:
     part between the embedding and the head, once per time its layer is in the run order."""
     def of_block(b):
         n = 0
-        for p in b.parts.values():
-            n += sum(2 * t.numel() for t in _tensors(p) if t.dim() == 2)
+        for p in list(b.parts.values()) + [b]:
+            own = getattr(p, "flops_per_token", None)       # a part whose tensors do not tell (experts, folded maps) counts itself
+            n += own() if own is not None else sum(2 * t.numel() for t in _tensors(p) if t.dim() == 2)
         return n
     return float(sum(of_block(model.blocks[c.layer]) for c in model.calls))
 

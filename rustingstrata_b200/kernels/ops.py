@@ -119,6 +119,8 @@ def core():
         lib.rs_gated_linear_recurrence.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_int,
                                                    c_void_p, c_int, c_void_p, c_int, c_long, c_void_p, c_long, c_void_p,
                                                    c_void_p, c_int, c_int, c_float, c_void_p]
+        lib.rs_gated_linear_recurrence_chunked.argtypes = lib.rs_gated_linear_recurrence.argtypes[:-1] + [
+            c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.rs_latent_kv_write.argtypes = [c_void_p, c_long, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_int, c_int,
                                            c_void_p, c_int, c_long, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                            c_void_p, c_int, c_int, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int,
@@ -129,7 +131,8 @@ def core():
         lib.rs_grouped_linear_rows_per_tile.argtypes = [c_int]
         lib.rs_grouped_linear.argtypes = [c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
-        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_int, c_float, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
+        lib.rs_gather_rows.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_void_p]
+        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
                                        c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_void_p]
         _core = lib
     return _core
@@ -735,8 +738,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     planes = 1 if one_plane else 2
     if tuple(cache.shape[1:]) != (planes, n_kv, page_size, head_dim) or not cache.is_contiguous():
         raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [pages, {planes}, {n_kv}, {page_size}, {head_dim}]")
-    if head_dim % 16 or head_dim > 256:
-        raise KernelError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
+    if head_dim % 16 or head_dim > 576:
+        raise KernelError(f"attention: head size {head_dim} is not a multiple of 16 up to 576")
     if n_q % n_kv:
         raise KernelError(f"attention: {n_q} query heads are not a multiple of {n_kv} key/value heads")
     for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
@@ -1023,6 +1026,14 @@ def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
                           f"{I} -> {O} at strides {in_block_stride}, {out_block_stride}")
     if bias is not None and (bias.numel() != B * O or not bias.is_contiguous()):
         raise KernelError("block_linear: bias must hold blocks * out values")
+    if (bias is None and n_rows > MID_MAX_ROWS and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and out.dtype in (torch.bfloat16, torch.float32) and I % 8 == 0 and in_block_stride % 8 == 0
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and (O * I) % 8 == 0):
+        # a portion of a prompt: one tensor-core product per block over strided views of the same buffers
+        for b in range(B):
+            linear(x[:, b * in_block_stride: b * in_block_stride + I], weight[b],
+                   out[:, b * out_block_stride: b * out_block_stride + O], n_rows)
+        return
     _check(core().rs_block_linear(_ptr(x), dtype_code(x), x.stride(0), in_block_stride, _ptr(weight), dtype_code(weight),
                                   _ptr(bias), _any_code(bias), _ptr(out), dtype_code(out), out.stride(0), out_block_stride,
                                   n_rows, B, O, I, _stream()), "block_linear")
@@ -1030,11 +1041,15 @@ def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
 
 def gated_linear_recurrence(gates: torch.Tensor, u: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor],
                             lam: torch.Tensor, out: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
-                            slots: torch.Tensor, n_seqs: int, decay: float) -> None:
+                            slots: torch.Tensor, n_seqs: int, decay: float, chunks: Optional[dict] = None) -> None:
     """The real-gated linear recurrence of csrc/sequence_parts.cu over the step's packed sequences.
 
     gates float32 [T, 2W] (pre-activations of the recurrence gate, then of the input gate), u float32 [T, W], y float32
-    [T, W] view (pre-activation of the GELU branch), lam [W]; out [T, W]; state float32 [slots, >= W] view (updated)."""
+    [T, W] view (pre-activation of the GELU branch), lam [W]; out [T, W]; state float32 [slots, >= W] view (updated).
+
+    ``chunks``: for long portions, the step's tokens cut into chunks that run side by side (three kernels instead of one
+    thread per channel walking the whole portion): int32 device arrays ``chunk_seq``, ``chunk_start``, ``seq_first_chunk``,
+    ints ``n_chunks`` and ``chunk_len``, and ``work``, float32 with room for 3 * n_chunks * W values."""
     _cuda(gates, u, y, y_bias, lam, out, state, q_start, slots)
     W = lam.numel()
     for name, t in (("gates", gates), ("u", u), ("y", y)):
@@ -1050,10 +1065,22 @@ def gated_linear_recurrence(gates: torch.Tensor, u: torch.Tensor, y: torch.Tenso
         raise KernelError("gated_linear_recurrence: q_start and slots must be int32")
     if y_bias is not None and (y_bias.numel() != W or not y_bias.is_contiguous()):
         raise KernelError("gated_linear_recurrence: y_bias must hold one value per channel")
-    _check(core().rs_gated_linear_recurrence(_ptr(gates), gates.stride(0), _ptr(u), u.stride(0), _ptr(y), y.stride(0),
-                                             _ptr(y_bias), _any_code(y_bias), _ptr(lam), dtype_code(lam), _ptr(out),
-                                             dtype_code(out), out.stride(0), _ptr(state), state.stride(0), _ptr(q_start),
-                                             _ptr(slots), W, n_seqs, float(decay), _stream()), "gated_linear_recurrence")
+    args = (_ptr(gates), gates.stride(0), _ptr(u), u.stride(0), _ptr(y), y.stride(0), _ptr(y_bias), _any_code(y_bias), _ptr(lam),
+            dtype_code(lam), _ptr(out), dtype_code(out), out.stride(0), _ptr(state), state.stride(0), _ptr(q_start), _ptr(slots),
+            W, n_seqs, float(decay))
+    if chunks is not None and chunks["n_chunks"] > 0:
+        work = chunks["work"]
+        if work.dtype != torch.float32 or work.numel() < 3 * chunks["n_chunks"] * W or not work.is_contiguous():
+            raise KernelError("gated_linear_recurrence: the chunks' workspace is too small")
+        for k in ("chunk_seq", "chunk_start", "seq_first_chunk"):
+            if chunks[k].dtype != torch.int32:
+                raise KernelError(f"gated_linear_recurrence: {k} must be int32")
+        _check(core().rs_gated_linear_recurrence_chunked(*args, _ptr(chunks["chunk_seq"]), _ptr(chunks["chunk_start"]),
+                                                         _ptr(chunks["seq_first_chunk"]), chunks["n_chunks"],
+                                                         chunks["chunk_len"], _ptr(work), _stream()),
+               "gated_linear_recurrence_chunked", 3)
+        return
+    _check(core().rs_gated_linear_recurrence(*args, _stream()), "gated_linear_recurrence")
 
 
 def latent_kv_write(dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, q: torch.Tensor, q_head: int, q_nope: int,
@@ -1130,9 +1157,11 @@ def moe_route(ids: torch.Tensor, table: torch.Tensor, n_experts: int, n_tokens: 
 
 
 def grouped_linear(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch.Tensor, order: torch.Tensor,
-                   tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, small: bool) -> None:
+                   tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, small: bool,
+                   interleaved: bool = False) -> None:
     """One product per expert over the rows ``moe_route`` dealt to it.  Pair p reads row p // a_div of ``a`` and writes
-    row p of ``out``.  weight [E, N, K], or [E, 2N, K] when ``gated``: out = SiLU(a W[:N].T) * (a W[N:].T)."""
+    row p of ``out``.  weight [E, N, K], or [E, 2N, K] when ``gated``: out = SiLU(a Wg.T) * (a Wu.T) with the gate rows
+    first and the up rows behind them, or alternating (gate 2n, up 2n + 1) when ``interleaved``."""
     _cuda(a, weight, out, order, tiles, n_tiles)
     _rows_contiguous(a, "grouped_linear a")
     _rows_contiguous(out, "grouped_linear out")
@@ -1145,16 +1174,31 @@ def grouped_linear(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch
                           f"does not fit")
     _check(core().rs_grouped_linear(_ptr(a), dtype_code(a), a.stride(0), a_div, _ptr(weight), dtype_code(weight),
                                     weight.stride(0), _ptr(out), dtype_code(out), out.stride(0), _ptr(order), _ptr(tiles),
-                                    _ptr(n_tiles), max_tiles, N, K, 1 if gated else 0, 1 if small else 0, _stream()),
-           "grouped_linear")
+                                    _ptr(n_tiles), max_tiles, N, K, (2 if interleaved else 1) if gated else 0,
+                                    1 if small else 0, _stream()), "grouped_linear")
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor, out: torch.Tensor, n_rows: int, div: int = 1) -> None:
+    """out[i] = src[idx[i] // div] for i < n_rows (rows of one element type and width; idx int32 on the device)."""
+    _cuda(src, idx, out)
+    _rows_contiguous(src, "gather_rows src")
+    _rows_contiguous(out, "gather_rows out")
+    if src.dtype != out.dtype or src.shape[1] != out.shape[1] or idx.dtype != torch.int32 or idx.numel() < n_rows \
+            or out.shape[0] < n_rows or div < 1:
+        raise KernelError("gather_rows: rows of one type and width, int32 indices")
+    es = src.element_size()
+    _check(core().rs_gather_rows(_ptr(src), src.stride(0) * es, _ptr(idx), div, _ptr(out), out.stride(0) * es,
+                                 src.shape[1] * es, n_rows, _stream()), "gather_rows")
 
 
 def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tensor, n_tokens: int,
                 shared: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None,
-                gate_weight: Optional[torch.Tensor] = None) -> None:
-    """out[t] = weight * sum_k pair_out[t * top + k] + sigmoid(h[t] . gate_weight) * shared[t]  (float32 out; the
-    second term only with ``shared``, its factor 1 without ``gate_weight``)."""
-    _cuda(pair_out, out, shared, h, gate_weight)
+                gate_weight: Optional[torch.Tensor] = None, pair_row: Optional[torch.Tensor] = None) -> None:
+    """out[t] = weight * sum_k pair_out[row(t * top + k)] + sigmoid(h[t] . gate_weight) * shared[t]  (float32 out; the
+    second term only with ``shared``, its factor 1 without ``gate_weight``; row(p) = pair_row[p], or p without it)."""
+    _cuda(pair_out, out, shared, h, gate_weight, pair_row)
+    if pair_row is not None and (pair_row.dtype != torch.int32 or pair_row.numel() < n_tokens * top):
+        raise KernelError("moe_combine: pair_row must be int32 with tokens * top entries")
     _rows_contiguous(pair_out, "moe_combine pair_out")
     _rows_contiguous(out, "moe_combine out")
     n = out.shape[1]
@@ -1169,7 +1213,7 @@ def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tens
             _rows_contiguous(h, "moe_combine h")
             if gate_weight.numel() != n or not gate_weight.is_contiguous() or h.shape[1] != n:
                 raise KernelError("moe_combine: the gate reads h [T, n] with a weight of n values")
-    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), top, float(weight), _ptr(shared), _any_code(shared),
+    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), _ptr(pair_row), top, float(weight), _ptr(shared), _any_code(shared),
                                  0 if shared is None else shared.stride(0), _ptr(h if gate_weight is not None else None),
                                  _any_code(h), 0 if h is None else h.stride(0), _ptr(gate_weight), _any_code(gate_weight),
                                  _ptr(out), out.stride(0), n_tokens, n, _stream()), "moe_combine")

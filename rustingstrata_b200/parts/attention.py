@@ -46,6 +46,7 @@ class PagedAttention(Mixer):
     tensors: q_proj, k_proj, v_proj, o_proj, and q_norm, k_norm when qk_norm."""
     chain_safe = True
     one_plane = False      # a subclass whose cache row is key and value at once says True
+    max_head_dim = 256
 
     def __init__(self, spec, runtime, position=None):
         super().__init__(spec, runtime)
@@ -62,9 +63,9 @@ class PagedAttention(Mixer):
         self.position = position
         if self.n_heads % self.n_kv:
             raise ValueError(f"paged_attention: {self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
-        if self.hd % 16 or not 16 <= self.hd <= 256:
+        if self.hd % 16 or not 16 <= self.hd <= self.max_head_dim:
             raise ValueError(f"paged_attention: head size {self.hd} is not supported by the attention kernels "
-                             f"(multiples of 16 from 16 to 256)")
+                             f"(multiples of 16 from 16 to {self.max_head_dim})")
         self.q_width = self.n_heads * self.hd
         self.kv_width = self.n_kv * self.hd
         self.qkv_width = self.q_width + (2 * self.kv_width if self.kv_projection else 0)

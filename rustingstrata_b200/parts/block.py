@@ -129,6 +129,9 @@ class StreamReentryBlock(Block):
         self.step_row = tensors[t["step"]][self.index].contiguous()
         self.table = tensors[t["embedding"]]
 
+    def flops_per_token(self) -> float:
+        return 4.0 * self.hidden * self.hidden
+
     def forward(self, residual, ctx, call):
         T = ctx.n_tokens
         if ctx.owed is not None:

@@ -34,6 +34,7 @@ class LatentAttention(PagedAttention):
     parts (pairs (2i, 2i + 1): a part whose ``pairing`` is "interleaved")."""
     chain_safe = False
     one_plane = True
+    max_head_dim = 576     # what the CUDA-core attention takes: a 512-wide latent with a 64-wide rotated part
 
     def __init__(self, spec, runtime, position=None):
         p = spec.params
@@ -41,8 +42,8 @@ class LatentAttention(PagedAttention):
         self.rank = int(p["kv_rank"])
         self.q_head = self.dim + self.rot_dim
         self.lat = (self.rank + self.rot_dim + 15) // 16 * 16            # width of a cache row and of an absorbed query head
-        if self.lat > 256:
-            raise ValueError(f"latent_attention: kv_rank + rot_dim = {self.rank + self.rot_dim} exceeds the 256 values "
+        if self.lat > 576:
+            raise ValueError(f"latent_attention: kv_rank + rot_dim = {self.rank + self.rot_dim} exceeds the 576 values "
                              f"the attention kernels take per head")
         inner = PartSpec(spec.kind, {"hidden": p["hidden"], "n_heads": p["n_heads"], "n_kv_heads": 1, "head_dim": self.lat,
                                      "window": p.get("window"), "scale": p["scale"], "qk_norm": False}, spec.tensors)
@@ -81,8 +82,11 @@ class LatentAttention(PagedAttention):
     def cache_need(self):
         return CacheNeed(1, self.lat, self.window or None, planes=1)
 
-    def mixing_flops(self, q_lens, kv_lens) -> float:
-        return super().mixing_flops(q_lens, kv_lens)
+    def flops_per_token(self) -> float:
+        """Multiply-add flops of the products one token passes (the folded form the kernels run)."""
+        H = self.n_heads
+        return 2.0 * (H * self.q_head * self.hidden + (self.rank + self.rot_dim) * self.hidden + H * self.rank * self.dim
+                      + H * self.vdim * self.rank + self.hidden * H * self.vdim)
 
     def forward(self, h, residual, ctx: StepContext, call: CallInfo):
         rt, T, H = self.runtime, ctx.n_tokens, self.n_heads

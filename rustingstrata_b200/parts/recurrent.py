@@ -11,10 +11,11 @@ and S, both float32; gates, decays and the recurrence are float32 in both engine
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..kernels import ops
-from .base import CallInfo, Mixer, StepContext
+from .base import CallInfo, HostBatch, Mixer, StepContext
 from .registry import register_part
 from .spec import StateNeed, TensorNeed
 
@@ -44,6 +45,8 @@ class GatedLinearRecurrence(Mixer):
         rt.scratch("rglru_u", rt.max_batch_tokens, self.width, torch.float32)
         rt.scratch("rglru_gates", rt.max_batch_tokens, 2 * self.width, torch.float32)
         rt.scratch("rglru_act", rt.max_batch_tokens, self.width)
+        max_chunks = rt.max_batch_tokens // self.SCAN_CHUNK + rt.max_seqs
+        rt.scratch("rglru_scan", 1, 3 * max_chunks * self.width, torch.float32)
 
     def tensor_needs(self):
         t, W, B, bw = self.spec.tensors, self.width, self.blocks, self.bw
@@ -67,6 +70,28 @@ class GatedLinearRecurrence(Mixer):
     def state_need(self):
         return StateNeed(self.tail + self.width, "float32")
 
+    # Portions longer than SCAN_CHUNK tokens are cut into chunks that run side by side (the recurrence is linear in S,
+    # so a chunk is a map S -> A S + B); shorter ones, and single tokens, take one thread per channel.
+    SCAN_CHUNK = 64
+
+    def plan_key(self):
+        return ("recurrence_chunks", self.SCAN_CHUNK)
+
+    def build_plan(self, batch: HostBatch):
+        L = self.SCAN_CHUNK
+        if batch.bucketed or int(batch.q_lens.max()) <= L:
+            return {"n_chunks": 0}
+        per_seq = (batch.q_lens + L - 1) // L
+        first = np.zeros(batch.n_seqs + 1, np.int32)
+        np.cumsum(per_seq, out=first[1:])
+        seq = np.repeat(np.arange(batch.n_seqs, dtype=np.int32), per_seq)
+        start = (np.arange(int(first[-1]), dtype=np.int32) - np.repeat(first[:-1], per_seq)) * L
+        return {"chunk_seq": seq, "chunk_start": start.astype(np.int32), "seq_first_chunk": first, "n_chunks": int(first[-1]),
+                "chunk_len": L}
+
+    def flops_per_token(self) -> float:
+        return 2.0 * (3 * self.width * self.hidden + 2 * self.width * self.bw)
+
     def forward(self, h, residual, ctx: StepContext, call: CallInfo):
         rt, T, W = self.runtime, ctx.n_tokens, self.width
         yx = rt.get_scratch("rglru_yx", torch.float32)[:, : 2 * W]
@@ -80,6 +105,8 @@ class GatedLinearRecurrence(Mixer):
                        in_bias=self.x_bias, bias=self.conv_bias)
         ops.block_linear(u, self.w_r, gates[:, :W], T, self.bw, self.bw, bias=self.b_r)
         ops.block_linear(u, self.w_i, gates[:, W:], T, self.bw, self.bw, bias=self.b_i)
+        plan = ctx.plans[self.plan_key()]
+        chunks = dict(plan, work=rt.get_scratch("rglru_scan", torch.float32).view(-1)) if plan["n_chunks"] else None
         ops.gated_linear_recurrence(gates, u, yx[:, :W], self.y_bias, self.lam, act, state[:, self.tail:], ctx.q_start,
-                                    ctx.state_slots, ctx.n_seqs, self.decay)
+                                    ctx.state_slots, ctx.n_seqs, self.decay, chunks=chunks)
         ops.linear(act, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)
