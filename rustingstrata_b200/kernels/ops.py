@@ -344,6 +344,11 @@ def bf16lib():
                                                 c_int, c_float, c_void_p, c_void_p]
         lib.rs_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
+        lib.rs_attention_latent_supported.argtypes = [c_int, c_int, c_int]
+        lib.rs_attention_latent_q_per_cta.argtypes = [c_int]
+        lib.rs_attention_latent_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_void_p,
+                                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                                 c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_attention_prefill_bf16_supported.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16_q_per_cta.argtypes = [c_int, c_int]
         _bf16 = lib
@@ -892,6 +897,49 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
         _stream()), "attention_decode_bf16", 2)
 
 
+def attention_latent_ok(dtype: torch.dtype, n_heads: int, lat: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel of latent attention takes this shape (bfloat16, rows a multiple of 16 up to 576)."""
+    return dtype == torch.bfloat16 and bool(bf16lib().rs_attention_latent_supported(n_heads, lat, page_size))
+
+
+def attention_latent_q_per_cta(n_heads: int) -> int:
+    """Query tokens per work item of the portion form of :func:`attention_latent`."""
+    return int(bf16lib().rs_attention_latent_q_per_cta(n_heads))
+
+
+def attention_latent(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_heads: int, lat: int,
+                     page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor, split_keys: int = 128,
+                     max_splits: int = 1, split_start: Optional[torch.Tensor] = None, total_splits: int = 0,
+                     partial: Optional[torch.Tensor] = None) -> None:
+    """Attention of ``n_heads`` query heads over a one-plane cache [pages, 1, 1, page_size, lat] whose rows are key and
+    value at once, on the tensor cores (csrc/attention_latent_mma.cu).  ``work``: (sequence, first query) tiles of
+    :func:`attention_latent_q_per_cta` tokens, or with ``decode`` one sequence per entry, the keys cut into splits whose
+    partial results (layout of :func:`attention_simt`) are merged by a second kernel."""
+    _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
+        raise KernelError("attention_latent: q, out and cache must be bfloat16 and the cache contiguous")
+    if tuple(cache.shape[1:]) != (1, 1, page_size, lat):
+        raise KernelError(f"attention_latent: cache shape {tuple(cache.shape)} is not [pages, 1, 1, {page_size}, {lat}]")
+    if q.shape[1] < n_heads * lat or out.shape[1] < n_heads * lat:
+        raise KernelError("attention_latent: q and out must hold heads * lat columns")
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len), ("work", work)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"attention_latent: {name} must be int32")
+    slots = 0
+    if decode:
+        if split_start is None or split_start.dtype != torch.int32:
+            raise KernelError("attention_latent: the split form needs int32 split_start")
+        slots = _partial_slots(partial, total_splits, n_heads, lat, "attention_latent")
+    _check(bf16lib().rs_attention_latent_bf16(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
+        _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_heads, lat, int(window),
+        float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start), _ptr(partial), slots, _ptr(status),
+        _stream()), "attention_latent", 2 if decode else 1)
+
+
 def attention_decode_items(split_start: torch.Tensor, n_work: int, n_kv: int, max_splits: int, items: torch.Tensor) -> None:
     """items[id] for every live (sequence, kv head, split) of a step of single tokens, id as the tensor-core decode
     kernel counts them; ``items`` int32 with room for split_start[n_work] * n_kv entries (n_work * n_kv * max_splits
@@ -1010,6 +1058,10 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, state: 
                                 1 if add_input else 0, n_tokens, n_seqs, _stream()), "short_conv", 2 if taps > 1 else 1)
 
 
+BLOCK_LINEAR_TC_ELEMENTS = 1 << 17     # blocks of fewer weights stay on the one-launch CUDA-core kernel: a tensor-core
+                                        # product per block costs about 13 us a launch whatever its size
+
+
 def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, in_block_stride: int,
                  out_block_stride: int, bias: Optional[torch.Tensor] = None) -> None:
     """out[t, b * out_block_stride + o] = bias[b, o] + sum_i weight[b, o, i] * x[t, b * in_block_stride + i]: one small
@@ -1028,7 +1080,8 @@ def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
         raise KernelError("block_linear: bias must hold blocks * out values")
     if (bias is None and n_rows > MID_MAX_ROWS and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and out.dtype in (torch.bfloat16, torch.float32) and I % 8 == 0 and in_block_stride % 8 == 0
-            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and (O * I) % 8 == 0):
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and (O * I) % 8 == 0
+            and O * I >= BLOCK_LINEAR_TC_ELEMENTS):
         # a portion of a prompt: one tensor-core product per block over strided views of the same buffers
         for b in range(B):
             linear(x[:, b * in_block_stride: b * in_block_stride + I], weight[b],

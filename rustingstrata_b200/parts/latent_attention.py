@@ -20,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .attention import PagedAttention
+from .attention import SPLIT_KEYS, PagedAttention
 from .base import CallInfo, StepContext
 from .registry import register_part
 from .spec import CacheNeed, PartSpec, TensorNeed
@@ -49,6 +49,7 @@ class LatentAttention(PagedAttention):
                                      "window": p.get("window"), "scale": p["scale"], "qk_norm": False}, spec.tensors)
         super().__init__(inner, runtime, position)
         self.spec = spec
+        self._tensor_cores = None
         self.latent_eps = float(p["eps"])
         if position is not None and getattr(position, "cos_sin", None) is not None:
             if getattr(position, "pairing", "") != "interleaved":
@@ -81,6 +82,36 @@ class LatentAttention(PagedAttention):
 
     def cache_need(self):
         return CacheNeed(1, self.lat, self.window or None, planes=1)
+
+    @property
+    def tensor_cores(self) -> bool:
+        """Whether the tensor-core kernel of latent attention runs (the bfloat16 engine); else the CUDA-core kernel."""
+        if self._tensor_cores is None:
+            self._tensor_cores = ops.attention_latent_ok(self.runtime.dtype, self.n_heads, self.lat, self.runtime.page_size)
+        return self._tensor_cores
+
+    def plan_key(self):
+        if self.q_per_cta is None and self.tensor_cores:
+            self.q_per_cta = ops.attention_latent_q_per_cta(self.n_heads)
+        return super().plan_key()
+
+    def _attend(self, q, ctx: StepContext, call: CallInfo):
+        if not self.tensor_cores:
+            return super()._attend(q, ctx, call)
+        rt = self.runtime
+        out = rt.get_scratch("attn_out")[:, : self.q_width]
+        plan = ctx.plans[self.plan_key()]
+        common = dict(q=q, out=out, cache=call.cache, block_table=ctx.block_tables[call.cache_group], q_start=ctx.q_start,
+                      kv_len=ctx.kv_len, n_heads=self.n_heads, lat=self.lat, page_size=rt.page_size, window=self.window,
+                      scale=self.scale, status=ctx.status)
+        if plan["n_prefill"]:
+            ops.attention_latent(work=plan["prefill_work"], n_work=plan["n_prefill"], decode=False, **common)
+        if plan["n_decode"]:
+            ops.attention_latent(work=plan["decode_work"], n_work=plan["n_decode"], decode=True, split_keys=SPLIT_KEYS,
+                                 max_splits=plan["max_splits"], split_start=plan["split_start"],
+                                 total_splits=plan["total_splits"], partial=rt.get_scratch("attn_partial", torch.float32),
+                                 **common)
+        return out
 
     def flops_per_token(self) -> float:
         """Multiply-add flops of the products one token passes (the folded form the kernels run)."""

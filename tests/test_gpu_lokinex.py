@@ -375,3 +375,59 @@ def test_kernels_of_the_new_parts_against_torch():
     assert torch.allclose(oc.cpu(), torch.cat([want0, want1]), atol=1e-5)
     assert torch.allclose(state[2].cpu().reshape(taps - 1, C), xin[1:4], atol=0)
     assert torch.allclose(state[0].cpu().reshape(taps - 1, C), xin[8:11], atol=0)
+
+
+@pytest.mark.parametrize("heads,lat,page", [(6, 80, 16), (16, 576, 16), (3, 48, 8), (20, 128, 32), (1, 16, 4)])
+def test_tensor_core_latent_attention_against_torch(heads, lat, page):
+    """The tensor-core kernel of latent attention (portions and the split form) against a plain float32 computation on
+    the same bfloat16 inputs: sequences of unequal length, portions that start in the middle of a page, single tokens
+    beside them, with and without a window."""
+    from rustingstrata_b200.kernels import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(heads * 1000 + lat)
+    kv_lens = [150, 37, 300, 1, 129, 64]
+    q_lens = [150, 5, 1, 1, 1, 33]                  # whole prompt, a portion, three single tokens, a portion
+    n_pages = sum((n + page - 1) // page for n in kv_lens) + 3
+    cache = (torch.randn(n_pages, 1, 1, page, lat, generator=g) * 0.7).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max((n + page - 1) // page for n in kv_lens)
+    table = torch.full((len(kv_lens), width), -1, dtype=torch.int32)
+    at = 0
+    for s, n in enumerate(kv_lens):
+        for b in range((n + page - 1) // page):
+            table[s, b] = perm[at]
+            at += 1
+    T = sum(q_lens)
+    q = (torch.randn(T, heads * lat, generator=g) * 0.5).to(torch.bfloat16)
+    q_start = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    scale = 1.7 / np.sqrt(lat)
+    for window in (0, 50):
+        # plain float32
+        want = torch.zeros(T, heads, lat)
+        for s, (n, ql) in enumerate(zip(kv_lens, q_lens)):
+            rows = torch.stack([cache[table[s, k // page], 0, 0, k % page] for k in range(n)]).float()       # [n, lat]
+            for j in range(ql):
+                pos = n - ql + j
+                lo = max(0, pos - window + 1) if window else 0
+                qq = q[q_start[s] + j].float().reshape(heads, lat)
+                pr = torch.softmax(qq @ rows[lo:pos + 1].T * scale, dim=-1)
+                want[q_start[s] + j] = pr @ rows[lo:pos + 1]
+        qpc = ops.attention_latent_q_per_cta(heads)
+        pre = [(s, o) for s, ql in enumerate(q_lens) if ql > 1 for o in range(0, ql, qpc)]
+        dec = [s for s, ql in enumerate(q_lens) if ql == 1]
+        lo = [max(0, kv_lens[s] - window) if window else 0 for s in dec]
+        splits = [(kv_lens[s] + 127) // 128 - l // 128 for s, l in zip(dec, lo)]
+        split_start = torch.tensor(np.concatenate([[0], np.cumsum(splits)]), dtype=torch.int32, device=dev)
+        out = torch.zeros(T, heads * lat, dtype=torch.bfloat16, device=dev)
+        partial = torch.empty(sum(splits) * heads * (lat + 2), dtype=torch.float32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        common = dict(q=q.to(dev), out=out, cache=cache.to(dev), block_table=table.to(dev), q_start=q_start.to(dev),
+                      kv_len=torch.tensor(kv_lens, dtype=torch.int32, device=dev), n_heads=heads, lat=lat, page_size=page,
+                      window=window, scale=scale, status=status)
+        ops.attention_latent(work=torch.tensor(pre, dtype=torch.int32, device=dev).reshape(-1), n_work=len(pre), decode=False, **common)
+        ops.attention_latent(work=torch.tensor(dec, dtype=torch.int32, device=dev), n_work=len(dec), decode=True, split_keys=128,
+                             max_splits=max(splits), split_start=split_start, total_splits=sum(splits), partial=partial, **common)
+        assert int(status.cpu()[0]) == 0
+        got = out.float().cpu().reshape(T, heads, lat)
+        err = (got - want).abs().max().item() / want.abs().max().item()
+        assert err < 1.5e-2, f"heads {heads} lat {lat} window {window}: {err:.3e}"
