@@ -389,7 +389,7 @@ class OpTimer:
     launchers (eager steps only), summed per name after a synchronisation."""
     NAMES = ("embed", "rmsnorm", "rmsnorm_add", "concat_embed", "short_conv", "block_linear", "gated_linear_recurrence",
              "gated_linear_recurrence_gates", "latent_kv_write", "relu_squared", "moe_route", "grouped_linear", "moe_combine",
-             "gather_rows", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
+             "grouped_gemm_mma", "attention_latent", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
              "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand")
 
     def __init__(self):

@@ -1,0 +1,137 @@
+// One launch for the products of all experts of a mixture, on the warp-level tensor cores (mma.sync m16n8k16,
+// bfloat16 operands, float32 accumulation): the bfloat16 engine's form of the grouped product in moe_simt.cu, with
+// the same work list (moe_route: the step's (token, k) pairs sorted by expert and cut into row tiles of 64).
+//
+// A CTA of 4 warps takes one row tile of one expert and 64 rows of the expert's matrix; it gathers its input rows
+// through the sorted list (pair p reads row p / a_div of A), streams A and W in steps of 32 of k through two
+// shared-memory buffers with cp.async, and writes every pair's result to the pair's own row of the output.  A warp owns
+// 32 x 32 of the tile.  Epilogues: plain store (float32 or bfloat16), or SiLU(gate) * up for a matrix whose rows
+// alternate gate, up: the two lie in neighbouring accumulator columns of one thread, and the output has half the columns.
+// Every output element accumulates k in ascending order, whatever else is in the batch.
+#include "mma_helpers.cuh"
+
+namespace {
+constexpr int BM = 64, BN = 64, BK = 32, PITCH = BK + 8, THREADS = 128;
+
+struct GroupedMmaParams {
+    const __nv_bfloat16* a; long a_stride; int a_div;
+    const __nv_bfloat16* w; long w_expert_stride; int w_rows;      // [E][w_rows][K]
+    void* out; int out_dt; long out_stride;
+    const int* order; const int* tiles; const int* n_tiles;
+    int K, gated;
+};
+
+__global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const GroupedMmaParams p) {
+    if ((int)blockIdx.y >= p.n_tiles[0]) return;
+    __shared__ __align__(16) __nv_bfloat16 As[2][BM][PITCH];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][BN][PITCH];
+    __shared__ int pair_of_row[BM];
+    const int e = p.tiles[3 * blockIdx.y], row0 = p.tiles[3 * blockIdx.y + 1], rows = p.tiles[3 * blockIdx.y + 2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * BN;
+    if (tid < BM) pair_of_row[tid] = tid < rows ? p.order[row0 + tid] : -1;
+    __syncthreads();
+    const __nv_bfloat16* wbase = p.w + (size_t)e * p.w_expert_stride;
+
+    auto load = [&](int buf, int k0) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int i = tid + q * THREADS;               // 256 chunks of 16 bytes per operand tile
+            const int r = i >> 2, ch = i & 3;
+            const int k = k0 + ch * 8;
+            const int pr = pair_of_row[r];
+            if (pr >= 0 && k < p.K) cp_async16(smem_addr(&As[buf][r][ch * 8]), p.a + (size_t)(pr / p.a_div) * p.a_stride + k);
+            else *reinterpret_cast<uint4*>(&As[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
+            const int gn = n0 + r;
+            if (gn < p.w_rows && k < p.K) cp_async16(smem_addr(&Ws[buf][r][ch * 8]), wbase + (size_t)gn * p.K + k);
+            else *reinterpret_cast<uint4*>(&Ws[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
+        }
+    };
+
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f; }
+    const int m_base = (warp >> 1) * 32, n_base = (warp & 1) * 32;
+    const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
+    const int n_steps = (p.K + BK - 1) / BK;
+    load(0, 0);
+    cp_async_commit();
+    for (int s = 0; s < n_steps; ++s) {
+        if (s + 1 < n_steps) {
+            load((s + 1) & 1, (s + 1) * BK);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int buf = s & 1;
+#pragma unroll
+        for (int kk = 0; kk < BK; kk += 16) {
+            uint32_t a[2][4], b[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(smem_addr(&As[buf][m_base + i * 16 + a_row][kk + a_col]), a[i][0], a[i][1], a[i][2], a[i][3]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                ldmatrix_x4(smem_addr(&Ws[buf][n_base + j * 16 + b_row][kk + b_col]), b[2 * j][0], b[2 * j][1], b[2 * j + 1][0],
+                            b[2 * j + 1][1]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma16816(acc[i][j], a[i], b[j][0], b[j][1]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int pr = pair_of_row[m_base + i * 16 + (lane >> 2) + 8 * half];
+            if (pr < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int gn = n0 + n_base + j * 8 + (lane & 3) * 2;
+                const float c0 = acc[i][j][2 * half], c1 = acc[i][j][2 * half + 1];
+                if (p.gated) {
+                    if (gn + 1 < p.w_rows) {
+                        const float v = silu_mul_fast(c0, c1);
+                        const size_t o = (size_t)pr * p.out_stride + (gn >> 1);
+                        if (p.out_dt == RS_F32) reinterpret_cast<float*>(p.out)[o] = v;
+                        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+                    }
+                } else {
+                    const size_t o = (size_t)pr * p.out_stride + gn;
+                    if (p.out_dt == RS_F32) {
+                        float* dst = reinterpret_cast<float*>(p.out) + o;
+                        if (gn < p.w_rows) dst[0] = c0;
+                        if (gn + 1 < p.w_rows) dst[1] = c1;
+                    } else {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+                        if (gn < p.w_rows) dst[0] = __float2bfloat16_rn(c0);
+                        if (gn + 1 < p.w_rows) dst[1] = __float2bfloat16_rn(c1);
+                    }
+                }
+            }
+        }
+}
+}  // namespace
+
+RS_EXPORT int rs_grouped_gemm_mma_rows_per_tile() { return BM; }
+
+// a: bfloat16 [*, K] rows 16-byte aligned; w: bfloat16 [E][w_rows][K]; out: [pairs, w_rows] (or w_rows / 2 when gated,
+// the rows of w alternating gate, up).  K a multiple of 8.
+RS_EXPORT int rs_grouped_gemm_mma(const void* a, long a_stride, int a_div, const void* w, long w_expert_stride, int w_rows,
+                                  void* out, int out_dt, long out_stride, const int* order, const int* tiles,
+                                  const int* n_tiles, int max_tiles, int K, int gated, void* stream) {
+    if (max_tiles <= 0 || w_rows <= 0) return 0;
+    if (K <= 0 || K % 8 || a_stride % 8 || w_expert_stride % 8 || ((size_t)a & 15) || ((size_t)w & 15) || (gated && w_rows % 2))
+        return (int)cudaErrorInvalidValue;
+    GroupedMmaParams p{(const __nv_bfloat16*)a, a_stride, a_div, (const __nv_bfloat16*)w, w_expert_stride, w_rows, out, out_dt,
+                       out_stride, order, tiles, n_tiles, K, gated};
+    grouped_gemm_mma_kernel<<<dim3((w_rows + BN - 1) / BN, max_tiles), THREADS, 0, (cudaStream_t)stream>>>(p);
+    return rs_launch_result();
+}

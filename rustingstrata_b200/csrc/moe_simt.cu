@@ -250,32 +250,9 @@ RS_EXPORT int rs_grouped_linear(const void* a, int a_dt, long a_stride, int a_di
     return rs_launch_result();
 }
 
-// out[i, :] = src[idx[i] / div, :] (rows of n elements of `es` bytes)
-__global__ void gather_rows_kernel(const unsigned char* __restrict__ src, long src_stride_bytes, const int* __restrict__ idx,
-                                   int div, unsigned char* __restrict__ out, long out_stride_bytes, int row_bytes) {
-    const unsigned char* s = src + (size_t)(idx[blockIdx.x] / div) * src_stride_bytes;
-    unsigned char* o = out + (size_t)blockIdx.x * out_stride_bytes;
-    if (row_bytes % 16 == 0 && ((size_t)s & 15) == 0 && ((size_t)o & 15) == 0) {
-        for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
-            reinterpret_cast<uint4*>(o)[i] = reinterpret_cast<const uint4*>(s)[i];
-    } else {
-        for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) o[i] = s[i];
-    }
-}
-
-RS_EXPORT int rs_gather_rows(const void* src, long src_stride_bytes, const int* idx, int div, void* out,
-                             long out_stride_bytes, int row_bytes, int n_rows, void* stream) {
-    if (n_rows <= 0) return 0;
-    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const unsigned char*)src, src_stride_bytes, idx, div,
-                                                                (unsigned char*)out, out_stride_bytes, row_bytes);
-    return rs_launch_result();
-}
-
-// out[t, :] = weight * sum_k pair_out[row(t * top + k), :] + sigmoid(h[t, :] . gate_w) * shared[t, :],
-// row(p) = pair_row ? pair_row[p] : p
+// out[t, :] = weight * sum_k pair_out[t * top + k, :] + sigmoid(h[t, :] . gate_w) * shared[t, :]
 // (shared == null: no shared expert).  out is float32 [T, n].
-__global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair_stride, const int* __restrict__ pair_row,
-                                   int top, float weight,
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair_stride, int top, float weight,
                                    const void* __restrict__ shared, int shared_dt, long shared_stride,
                                    const void* __restrict__ h, int h_dt, long h_stride, const void* __restrict__ gate_w,
                                    int gate_dt, float* __restrict__ out, long out_stride, int n) {
@@ -293,21 +270,18 @@ __global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair
     }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int pr = t * top + k;
-            v += pair_out[(size_t)(pair_row != nullptr ? pair_row[pr] : pr) * pair_stride + i];
-        }
+        for (int k = 0; k < top; ++k) v += pair_out[(size_t)(t * top + k) * pair_stride + i];
         v *= weight;
         if (shared != nullptr) v = fmaf(gate, load_any(shared, shared_dt, (size_t)t * shared_stride + i), v);
         out[(size_t)t * out_stride + i] = v;
     }
 }
 
-RS_EXPORT int rs_moe_combine(const float* pair_out, long pair_stride, const int* pair_row, int top, float weight, const void* shared,
+RS_EXPORT int rs_moe_combine(const float* pair_out, long pair_stride, int top, float weight, const void* shared,
                              int shared_dt, long shared_stride, const void* h, int h_dt, long h_stride, const void* gate_w,
                              int gate_dt, float* out, long out_stride, int n_tokens, int n, void* stream) {
     if (n_tokens <= 0) return 0;
-    moe_combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(pair_out, pair_stride, pair_row, top, weight, shared, shared_dt,
+    moe_combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(pair_out, pair_stride, top, weight, shared, shared_dt,
                                                                   shared_stride, h, h_dt, h_stride, gate_w, gate_dt, out,
                                                                   out_stride, n);
     return rs_launch_result();

@@ -253,8 +253,7 @@ class ModelRunner:
             raise StepError("device_tokens must be int32 on the device with one id per token")
         graphable = self.use_graphs and self.model.capturable and bool((q_lens == 1).all()) and on_layer is None
         try:
-            ctx, layout = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R, graphable,
-                                              host_tokens=device_tokens is None)
+            ctx, layout = self._build_context(entries, tokens, q_lens, old, kv_lens, T, R, graphable)
             ctx.on_layer = on_layer
 
             chain = (ops.CHAIN_DECODE and self.dtype == torch.bfloat16 and T <= ops.chain_max_rows()
@@ -315,7 +314,7 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    def _build_context(self, entries, tokens, q_lens, old, kv_lens, T, R, bucketed=False, host_tokens=True):
+    def _build_context(self, entries, tokens, q_lens, old, kv_lens, T, R, bucketed=False):
         """The step's index arrays in one pinned buffer, uploaded with one copy.  Returns the context and a
         hashable description of the layout (sizes and host scalars): equal layouts put every array at the
         same device address, which is what lets a captured step be replayed."""
@@ -346,8 +345,7 @@ class ModelRunner:
             tables.append(tab)
         batch = HostBatch(n_tokens=T, n_seqs=S, q_lens=q_lens, kv_lens=kv_lens.astype(np.int32), q_start=q_start,
                           state_slots=slots, first_step=(old == 0).astype(np.int32), page_size=self.page_size,
-                          max_blocks=[t.shape[1] for t in tables], bucketed=bucketed,
-                          token_ids=tokens.astype(np.int32) if host_tokens else None)
+                          max_blocks=[t.shape[1] for t in tables], bucketed=bucketed)
         plans = self.model.plan(batch)
 
         arrays = [("token_ids", tokens.astype(np.int32)), ("positions", positions.reshape(-1)), ("seq_of_token", seq_of_token),

@@ -131,8 +131,7 @@ def core():
         lib.rs_grouped_linear_rows_per_tile.argtypes = [c_int]
         lib.rs_grouped_linear.argtypes = [c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
-        lib.rs_gather_rows.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_void_p]
-        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
+        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_int, c_float, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
                                        c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_void_p]
         _core = lib
     return _core
@@ -344,6 +343,8 @@ def bf16lib():
                                                 c_int, c_float, c_void_p, c_void_p]
         lib.rs_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
+        lib.rs_grouped_gemm_mma.argtypes = [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_void_p,
+                                            c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_latent_supported.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_latent_q_per_cta.argtypes = [c_int]
         lib.rs_attention_latent_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_void_p,
@@ -1231,27 +1232,39 @@ def grouped_linear(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch
                                     1 if small else 0, _stream()), "grouped_linear")
 
 
-def gather_rows(src: torch.Tensor, idx: torch.Tensor, out: torch.Tensor, n_rows: int, div: int = 1) -> None:
-    """out[i] = src[idx[i] // div] for i < n_rows (rows of one element type and width; idx int32 on the device)."""
-    _cuda(src, idx, out)
-    _rows_contiguous(src, "gather_rows src")
-    _rows_contiguous(out, "gather_rows out")
-    if src.dtype != out.dtype or src.shape[1] != out.shape[1] or idx.dtype != torch.int32 or idx.numel() < n_rows \
-            or out.shape[0] < n_rows or div < 1:
-        raise KernelError("gather_rows: rows of one type and width, int32 indices")
-    es = src.element_size()
-    _check(core().rs_gather_rows(_ptr(src), src.stride(0) * es, _ptr(idx), div, _ptr(out), out.stride(0) * es,
-                                 src.shape[1] * es, n_rows, _stream()), "gather_rows")
+def grouped_gemm_mma_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the tensor-core grouped product takes these operands: bfloat16, k a multiple of 8, rows 16-byte aligned."""
+    return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 3 and weight.is_contiguous()
+            and weight.shape[2] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1 and a.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
+
+
+def grouped_gemm_mma(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch.Tensor, order: torch.Tensor,
+                     tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool) -> None:
+    """The grouped product of :func:`grouped_linear` on the tensor cores (csrc/grouped_gemm_mma.cu), for the row tiles
+    of ``GROUPED_ROWS_TILED`` that ``moe_route`` lists.  ``gated``: the rows of every expert's matrix alternate gate, up
+    and out = SiLU(gate) * up has half as many columns as the matrix has rows."""
+    _cuda(a, weight, out, order, tiles, n_tiles)
+    _rows_contiguous(out, "grouped_gemm_mma out")
+    if not grouped_gemm_mma_ok(a, weight):
+        raise KernelError("grouped_gemm_mma: bfloat16 operands with 16-byte aligned rows and k a multiple of 8")
+    E, rows, K = weight.shape
+    if a.shape[1] != K or out.shape[1] != (rows // 2 if gated else rows) or (gated and rows % 2) or max_tiles * 3 > tiles.numel():
+        raise KernelError(f"grouped_gemm_mma: a {tuple(a.shape)} x weight {tuple(weight.shape)} -> out {tuple(out.shape)} "
+                          f"does not fit")
+    if int(bf16lib().rs_grouped_gemm_mma_rows_per_tile()) != GROUPED_ROWS_TILED:
+        raise KernelError("grouped_gemm_mma: the compiled kernel's row tile differs from the launcher's")
+    _check(bf16lib().rs_grouped_gemm_mma(_ptr(a), a.stride(0), a_div, _ptr(weight), weight.stride(0), rows, _ptr(out),
+                                         dtype_code(out), out.stride(0), _ptr(order), _ptr(tiles), _ptr(n_tiles), max_tiles,
+                                         K, 1 if gated else 0, _stream()), "grouped_gemm_mma")
 
 
 def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tensor, n_tokens: int,
                 shared: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None,
-                gate_weight: Optional[torch.Tensor] = None, pair_row: Optional[torch.Tensor] = None) -> None:
-    """out[t] = weight * sum_k pair_out[row(t * top + k)] + sigmoid(h[t] . gate_weight) * shared[t]  (float32 out; the
-    second term only with ``shared``, its factor 1 without ``gate_weight``; row(p) = pair_row[p], or p without it)."""
-    _cuda(pair_out, out, shared, h, gate_weight, pair_row)
-    if pair_row is not None and (pair_row.dtype != torch.int32 or pair_row.numel() < n_tokens * top):
-        raise KernelError("moe_combine: pair_row must be int32 with tokens * top entries")
+                gate_weight: Optional[torch.Tensor] = None) -> None:
+    """out[t] = weight * sum_k pair_out[t * top + k] + sigmoid(h[t] . gate_weight) * shared[t]  (float32 out; the
+    second term only with ``shared``, its factor 1 without ``gate_weight``)."""
+    _cuda(pair_out, out, shared, h, gate_weight)
     _rows_contiguous(pair_out, "moe_combine pair_out")
     _rows_contiguous(out, "moe_combine out")
     n = out.shape[1]
@@ -1266,7 +1279,7 @@ def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tens
             _rows_contiguous(h, "moe_combine h")
             if gate_weight.numel() != n or not gate_weight.is_contiguous() or h.shape[1] != n:
                 raise KernelError("moe_combine: the gate reads h [T, n] with a weight of n values")
-    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), _ptr(pair_row), top, float(weight), _ptr(shared), _any_code(shared),
+    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), top, float(weight), _ptr(shared), _any_code(shared),
                                  0 if shared is None else shared.stride(0), _ptr(h if gate_weight is not None else None),
                                  _any_code(h), 0 if h is None else h.stride(0), _ptr(gate_weight), _any_code(gate_weight),
                                  _ptr(out), out.stride(0), n_tokens, n, _stream()), "moe_combine")

@@ -85,7 +85,6 @@ class HostBatch:
     first_step: np.ndarray        # 1 where the sequence has no earlier tokens
     page_size: int
     max_blocks: List[int]         # per cache group: width of the block tables of this step
-    token_ids: Optional[np.ndarray] = None   # the step's token ids where the host knows them (not when they stay on the device)
     bucketed: bool = False        # the step may be captured in a CUDA graph: host scalars that become launch
                                   # shapes must be rounded up to buckets so that later steps can replay it
 

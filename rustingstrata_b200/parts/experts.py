@@ -9,11 +9,10 @@ kernel adds a token's pairs in ascending k together with the gated shared expert
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from ..kernels import ops
-from .base import FeedForward, HostBatch, StepContext
+from .base import FeedForward, StepContext
 from .registry import register_part
 from .spec import TensorNeed
 
@@ -55,8 +54,6 @@ class TableMoE(FeedForward):
     tensors: table [vocab, top]; expert_gate / expert_up / expert_down: name patterns with ``{e}`` for the expert's
     number; shared_gate, shared_up, shared_down, shared_scale [1, hidden] when there is a shared expert."""
     SMALL_PAIRS_PER_EXPERT = 4      # up to this many (token, k) pairs per expert on average the row-streaming form runs
-    HOST_ROUTED_PAIRS_PER_EXPERT = 24   # from this many on average, a prompt step whose ids the host knows sorts its pairs
-                                        # on the host and runs one tensor-core product per expert and projection
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -69,10 +66,9 @@ class TableMoE(FeedForward):
             raise ValueError(f"table_moe: top {self.top} of {self.n_experts} experts")
         rt = runtime
         pairs = rt.max_batch_tokens * self.top
-        # the row pitch of these two is the row's own width, so that rows of every expert's share stay 16-byte aligned
-        self.act_name, self.sorted_name = f"moe_act_{self.ff}", f"moe_sorted_in_{self.hidden}"
+        # the row pitch is the row's own width, so that the rows stay 16-byte aligned whatever other layers ask for
+        self.act_name = f"moe_act_{self.ff}"
         rt.scratch(self.act_name, pairs, self.ff)
-        rt.scratch(self.sorted_name, pairs, self.hidden)
         rt.scratch("moe_pair_out", pairs, self.hidden, torch.float32)
         rt.scratch("moe_order", 1, pairs, torch.int32)
         self.max_tiles_small = self._max_tiles(pairs, True)
@@ -107,15 +103,14 @@ class TableMoE(FeedForward):
         self.table = tensors[t["table"]].contiguous()
         # all experts in one tensor each: [E, gate rows then up rows, hidden] and [E, hidden, ff]
         g0 = tensors[t["expert_gate"].format(e=0)]
-        # bfloat16 engine with 16-byte aligned rows: gate and up rows alternate, the layout whose SiLU(gate) * up the
-        # tensor-core products apply in their epilogue; the grouped CUDA-core product reads either layout
+        # bfloat16 engine with 16-byte aligned rows: gate and up rows alternate, so that the tensor-core grouped product
+        # finds a gate and its up in neighbouring accumulator columns; else gate rows first, up rows behind them
         self.interleaved = (g0.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0
                             and self.ff % 8 == 0)
         join = (lambda g, u: torch.stack([g, u], dim=1).reshape(2 * self.ff, self.hidden)) if self.interleaved else \
             (lambda g, u: torch.cat([g, u], dim=0))
         self.w_gate_up = torch.stack([join(tensors[t["expert_gate"].format(e=e)], tensors[t["expert_up"].format(e=e)])
                                       for e in range(E)]).contiguous()
-        self.table_host = self.table.cpu().numpy()
         self.w_down = torch.stack([tensors[t["expert_down"].format(e=e)] for e in range(E)]).contiguous()
         if self.shared_ff:
             g, u = tensors[t["shared_gate"]], tensors[t["shared_up"]]
@@ -131,46 +126,12 @@ class TableMoE(FeedForward):
         """Multiply-add flops of one token: its ``top`` experts and the shared one."""
         return 2.0 * (3 * self.top * self.ff * self.hidden + 3 * self.shared_ff * self.hidden + (self.hidden if self.shared_ff else 0))
 
-    # ---------------------------------------------------------------- planning
-    def plan_key(self):
-        return ("table_moe", self.spec.tensors["table"])
-
-    def build_plan(self, batch: HostBatch):
-        """A prompt step whose ids the host knows, with enough pairs per expert: the pairs sorted by expert here."""
-        pairs = batch.n_tokens * self.top
-        if (batch.token_ids is None or batch.bucketed or not self.interleaved
-                or pairs < self.HOST_ROUTED_PAIRS_PER_EXPERT * self.n_experts):
-            return {"host_routed": 0}
-        experts = self.table_host[batch.token_ids].reshape(-1)
-        order = np.argsort(experts, kind="stable").astype(np.int32)              # sorted row -> pair id
-        row_of_pair = np.empty(pairs, np.int32)
-        row_of_pair[order] = np.arange(pairs, dtype=np.int32)
-        counts = np.bincount(experts, minlength=self.n_experts)
-        return {"host_routed": 1, "order": order, "row_of_pair": row_of_pair, "counts": tuple(int(c) for c in counts)}
-
-    def _forward_host_routed(self, h, plan, pair_out, ctx):
-        """One tensor-core product per expert and projection over the expert's rows of the sorted pairs."""
-        rt, P = self.runtime, ctx.n_tokens * self.top
-        x = rt.get_scratch(self.sorted_name)[:, : self.hidden]
-        act = rt.get_scratch(self.act_name)[:, : self.ff]
-        ops.gather_rows(h, plan["order"], x, P, div=self.top)
-        off = 0
-        for e, n in enumerate(plan["counts"]):
-            if n:
-                ops.linear_swiglu(x[off:off + n], self.w_gate_up[e], act[off:off + n], n, status=ctx.status)
-                ops.linear(act[off:off + n], self.w_down[e], pair_out[off:off + n], n, status=ctx.status)
-                off += n
-
     def forward(self, h, residual, ctx: StepContext):
         rt, T, top = self.runtime, ctx.n_tokens, self.top
         pairs = T * top
-        plan = ctx.plans[self.plan_key()]
-        if plan["host_routed"]:
-            pair_out = rt.get_scratch("moe_pair_out", torch.float32)[:, : self.hidden]
-            self._forward_host_routed(h, plan, pair_out, ctx)
-            self._shared_and_combine(h, residual, ctx, pair_out, plan["row_of_pair"])
-            return
-        small = pairs <= self.SMALL_PAIRS_PER_EXPERT * self.n_experts
+        # bfloat16 engine: one tensor-core launch per projection for all experts, whatever the step's size
+        tensor_cores = self.interleaved
+        small = not tensor_cores and pairs <= self.SMALL_PAIRS_PER_EXPERT * self.n_experts
         max_tiles = self._max_tiles(pairs, small)
         order = rt.get_scratch("moe_order", torch.int32).view(-1)
         tiles = rt.get_scratch("moe_tiles", torch.int32).view(-1)
@@ -178,13 +139,12 @@ class TableMoE(FeedForward):
         act = rt.get_scratch(self.act_name)[:, : self.ff]
         pair_out = rt.get_scratch("moe_pair_out", torch.float32)[:, : self.hidden]
         ops.moe_route(ctx.token_ids, self.table, self.n_experts, T, _ROWS_PER_TILE[small], order, tiles, n_tiles, ctx.status)
-        ops.grouped_linear(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True, small=small,
-                           interleaved=self.interleaved)
-        ops.grouped_linear(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, small=small)
-        self._shared_and_combine(h, residual, ctx, pair_out, None)
-
-    def _shared_and_combine(self, h, residual, ctx, pair_out, pair_row):
-        rt, T, top = self.runtime, ctx.n_tokens, self.top
+        if tensor_cores:
+            ops.grouped_gemm_mma(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True)
+            ops.grouped_gemm_mma(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False)
+        else:
+            ops.grouped_linear(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True, small=small)
+            ops.grouped_linear(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, small=small)
         shared_out = None
         if self.shared_ff:
             sact = rt.get_scratch("moe_shared_act")[:, : self.shared_ff]
@@ -198,11 +158,11 @@ class TableMoE(FeedForward):
             ops.linear(sact, self.w_shared_down, shared_out, T, status=ctx.status)
         if ctx.store_output:
             ops.moe_combine(pair_out, top, 1.0 / top, residual, T, shared=shared_out, h=h,
-                            gate_weight=self.w_shared_scale if self.shared_ff else None, pair_row=pair_row)
+                            gate_weight=self.w_shared_scale if self.shared_ff else None)
         else:
             delta = rt.get_scratch("moe_delta", torch.float32)[:, : self.hidden]
             ops.moe_combine(pair_out, top, 1.0 / top, delta, T, shared=shared_out, h=h,
-                            gate_weight=self.w_shared_scale if self.shared_ff else None, pair_row=pair_row)
+                            gate_weight=self.w_shared_scale if self.shared_ff else None)
             ops.residual_add(residual, delta, T)
 
 
