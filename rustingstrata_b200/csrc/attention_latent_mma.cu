@@ -21,7 +21,7 @@
 
 namespace {
 constexpr int KT = 64, ROWS = 16, WARPS = 8, THREADS = WARPS * 32, NT_MAX = 9, MAX_LAT = 576;
-constexpr int S_PITCH = KT + 4, P_PITCH = KT + 8;
+constexpr int S_PITCH = KT + 4, P_PITCH = KT + 8, MERGE_CACHED = 512;
 
 struct LatParams {
     const __nv_bfloat16* q; long q_stride;          // [tokens, q_stride], head h at h * lat
@@ -250,18 +250,37 @@ __global__ void latent_merge_kernel(const LatParams p) {
     }
     const float* base = p.partial + ((size_t)p.split_start[w] * p.n_heads + h) * (lat + 2);
     const size_t split_stride = (size_t)p.n_heads * (lat + 2);
+    // every thread takes the splits' maxima in (the loads are independent of each other), then the weights of up to
+    // MERGE_CACHED splits and the denominator are kept in shared memory; a sequence with more splits recomputes them
+    __shared__ float ws[MERGE_CACHED];
+    __shared__ float stats[2];
     float M = -INFINITY;
+#pragma unroll 4
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[s * split_stride + lat]);
-    __nv_bfloat16* dst = p.out + (size_t)p.q_start[seq] * p.out_stride + (size_t)h * lat;
-    for (int d = threadIdx.x; d < lat; d += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
+    if (threadIdx.x < 32) {
+        float den = 0.f;                                      // lanes take splits in turn, added lane by lane: a fixed order
+        for (int s = threadIdx.x; s < n_splits; s += 32) {
             const float* ps = base + s * split_stride;
             const float e = __expf(ps[lat] - M);
-            num = fmaf(ps[d], e, num);
+            if (s < MERGE_CACHED) ws[s] = e;
             den = fmaf(ps[lat + 1], e, den);
         }
-        dst[d] = __float2bfloat16_rn(num / den);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        if (threadIdx.x == 0) stats[0] = den;
+    }
+    __syncthreads();
+    const float inv = 1.0f / stats[0];
+    __nv_bfloat16* dst = p.out + (size_t)p.q_start[seq] * p.out_stride + (size_t)h * lat;
+    for (int d = threadIdx.x; d < lat; d += blockDim.x) {
+        float num = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) {
+            const float* ps = base + s * split_stride;
+            const float e = s < MERGE_CACHED ? ws[s] : __expf(ps[lat] - M);
+            num = fmaf(ps[d], e, num);
+        }
+        dst[d] = __float2bfloat16_rn(num * inv);
     }
 }
 

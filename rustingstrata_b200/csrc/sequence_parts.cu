@@ -150,6 +150,26 @@ __global__ void short_conv_state_kernel(const ConvParams p) {
     for (int k = 0; k < keep; ++k) tail[(size_t)k * p.C + c] = v[k];
 }
 
+// a step of single tokens: one thread per (sequence, channel) computes the output and moves the tail up, one kernel
+__global__ void short_conv_single_kernel(const ConvParams p) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)p.n_seqs * p.C) return;
+    const int s = (int)(idx / p.C), c = (int)(idx % p.C);
+    const int row0 = p.q_start[s];
+    float* tail = p.state + (size_t)p.slots[s] * p.state_stride;
+    const float x = conv_input(p, row0, 0, c, tail);
+    float acc = load_any(p.w, p.w_dt, (size_t)c * p.taps + p.taps - 1) * x;
+    for (int j = 0; j < p.taps - 1; ++j) {
+        const float v = tail[(size_t)j * p.C + c];
+        acc = fmaf(load_any(p.w, p.w_dt, (size_t)c * p.taps + j), v, acc);
+        if (j > 0) tail[(size_t)(j - 1) * p.C + c] = v;
+    }
+    if (p.taps > 1) tail[(size_t)(p.taps - 2) * p.C + c] = x;
+    if (p.bias != nullptr) acc += load_any(p.bias, p.bias_dt, c);
+    if (p.add_input) acc += x;
+    store_any(p.out, p.out_dt, (size_t)row0 * p.out_stride + c, acc);
+}
+
 RS_EXPORT int rs_short_conv(const void* in, int in_dt, long in_stride, const void* in_bias, int in_bias_dt, const void* w,
                             int w_dt, const void* bias, int bias_dt, void* out, int out_dt, long out_stride, float* state,
                             long state_stride, const int* seq_of_token, const int* q_start, const int* slots, int C,
@@ -159,6 +179,11 @@ RS_EXPORT int rs_short_conv(const void* in, int in_dt, long in_stride, const voi
     ConvParams p{in, in_dt, in_stride, in_bias, in_bias_dt, w, w_dt, bias, bias_dt, out, out_dt, out_stride, state,
                  state_stride, seq_of_token, q_start, slots, C, taps, add_input, n_tokens, n_seqs};
     cudaStream_t s = (cudaStream_t)stream;
+    if (n_tokens == n_seqs) {                     // every sequence brings one token
+        const long st = (long)n_seqs * C;
+        short_conv_single_kernel<<<(unsigned)((st + 255) / 256), 256, 0, s>>>(p);
+        return rs_launch_result();
+    }
     const long total = (long)n_tokens * C;
     short_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(p);
     cudaError_t e = cudaGetLastError();
@@ -232,6 +257,68 @@ __global__ void __launch_bounds__(256) block_linear_kernel(const BlockLinearPara
         }
     }
 }
+
+// the same for at most 8 rows (single tokens): the rows sit in shared memory as float32, a warp owns output columns
+// and reads their weight rows once, 16 bytes per lane and load where the weights are bfloat16 and aligned
+constexpr int BR_ROWS = 8, BR_COLS = 32, BR_KC = 512;
+
+__global__ void __launch_bounds__(256) block_linear_rows_kernel(const BlockLinearParams p) {
+    __shared__ float xs[BR_ROWS][BR_KC];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = blockIdx.y;
+    const int o0 = blockIdx.x * BR_COLS + warp * (BR_COLS / 8);
+    float acc[BR_COLS / 8][BR_ROWS];
+#pragma unroll
+    for (int c = 0; c < BR_COLS / 8; ++c)
+#pragma unroll
+        for (int r = 0; r < BR_ROWS; ++r) acc[c][r] = 0.f;
+    const bool vec = p.w_dt == RS_BF16 && p.I % 8 == 0 && ((size_t)p.w & 15) == 0;
+    for (int k0 = 0; k0 < p.I; k0 += BR_KC) {
+        __syncthreads();
+        const int kc = min(BR_KC, p.I - k0);
+        for (int i = tid; i < BR_ROWS * kc; i += 256) {
+            const int r = i / kc, kk = i - r * kc;
+            xs[r][kk] = r < p.T ? load_any(p.in, p.in_dt, (size_t)r * p.in_stride + (size_t)b * p.in_bs + k0 + kk) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < BR_COLS / 8; ++c) {
+            const int o = o0 + c;
+            if (o >= p.O) continue;
+            const size_t wrow = ((size_t)b * p.O + o) * p.I + k0;
+            if (vec) {
+                const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(p.w);
+                for (int kk = lane * 8; kk < kc; kk += 256) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wp + wrow + kk);
+                    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float w0 = __low2float(w2[q]), w1 = __high2float(w2[q]);
+#pragma unroll
+                        for (int r = 0; r < BR_ROWS; ++r) acc[c][r] = fmaf(xs[r][kk + 2 * q + 1], w1, fmaf(xs[r][kk + 2 * q], w0, acc[c][r]));
+                    }
+                }
+            } else {
+                for (int kk = lane; kk < kc; kk += 32) {
+                    const float w = load_any(p.w, p.w_dt, wrow + kk);
+#pragma unroll
+                    for (int r = 0; r < BR_ROWS; ++r) acc[c][r] = fmaf(xs[r][kk], w, acc[c][r]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < BR_COLS / 8; ++c) {
+        const int o = o0 + c;
+#pragma unroll
+        for (int r = 0; r < BR_ROWS; ++r) {
+            float v = warp_sum(acc[c][r]);
+            if (lane == 0 && o < p.O && r < p.T) {
+                if (p.bias != nullptr) v += load_any(p.bias, p.bias_dt, (size_t)b * p.O + o);
+                store_any(p.out, p.out_dt, (size_t)r * p.out_stride + (size_t)b * p.out_bs + o, v);
+            }
+        }
+    }
+}
 }  // namespace
 
 RS_EXPORT int rs_block_linear(const void* in, int in_dt, long in_stride, long in_bs, const void* w, int w_dt,
@@ -239,6 +326,10 @@ RS_EXPORT int rs_block_linear(const void* in, int in_dt, long in_stride, long in
                               int B, int O, int I, void* stream) {
     if (T <= 0 || B <= 0 || O <= 0) return 0;
     BlockLinearParams p{in, in_dt, in_stride, in_bs, w, w_dt, bias, bias_dt, out, out_dt, out_stride, out_bs, T, O, I};
+    if (T <= BR_ROWS) {
+        block_linear_rows_kernel<<<dim3((O + BR_COLS - 1) / BR_COLS, B), 256, 0, (cudaStream_t)stream>>>(p);
+        return rs_launch_result();
+    }
     dim3 grid((O + BL_BN - 1) / BL_BN, (T + BL_BM - 1) / BL_BM, B);
     block_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
     return rs_launch_result();
@@ -246,11 +337,12 @@ RS_EXPORT int rs_block_linear(const void* in, int in_dt, long in_stride, long in
 
 // --------------------------------------------------------------------------- gated linear recurrence
 // One thread per (sequence, channel) walks the sequence's tokens of this step in order:
-//   r = sigmoid(gates[t, c]), i = sigmoid(gates[t, W + c]), log a = -decay_c * r * softplus(lam[c]), a = exp(log a),
+//   r = sigmoid(gates[t, g(c)]), i = sigmoid(gates[t, g(c) + bw]) with g(c) = (c / bw) * 2 bw + c % bw (the gates of a
+//   block of bw channels lie together: its r, then its i), log a = -decay_c * r * softplus(lam[c]), a = exp(log a),
 //   S = a S + sqrt(1 - a^2) i u[t, c];  out[t, c] = S * gelu_tanh(y[t, c] + y_bias[c]).
 // S starts from the sequence's state slot (zero after admission) and is written back.
 struct RecurrenceParams {
-    const float* gates; long gates_stride;      // [T, 2W]: r pre-activations, then i
+    const float* gates; long gates_stride;      // [T, 2W]: per block of bw channels, bw r pre-activations, then bw of i
     const float* u; long u_stride;              // [T, W]
     const float* y; long y_stride;              // [T, W] pre-activation of the gating branch
     const void* y_bias; int y_bias_dt;
@@ -259,7 +351,10 @@ struct RecurrenceParams {
     float* state; long state_stride;
     const int* q_start; const int* slots;
     int W, n_seqs; float decay_c;
+    int bw;                                     // channels per block of the gates' layout (W: all r, then all i)
 };
+
+__device__ __forceinline__ int gate_index(const RecurrenceParams& p, int c) { return (c / p.bw) * 2 * p.bw + c % p.bw; }
 
 __global__ void gated_linear_recurrence_kernel(const RecurrenceParams p) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -270,10 +365,11 @@ __global__ void gated_linear_recurrence_kernel(const RecurrenceParams p) {
     float S = *sp;
     const float k = -p.decay_c * softplus_f32(load_any(p.lam, p.lam_dt, c));
     const float yb = p.y_bias != nullptr ? load_any(p.y_bias, p.y_bias_dt, c) : 0.f;
+    const int gi = gate_index(p, c);
     for (int li = 0; li < n; ++li) {
         const size_t t = (size_t)(row0 + li);
-        const float r = sigmoid_f32(p.gates[t * p.gates_stride + c]);
-        const float ig = sigmoid_f32(p.gates[t * p.gates_stride + p.W + c]);
+        const float r = sigmoid_f32(p.gates[t * p.gates_stride + gi]);
+        const float ig = sigmoid_f32(p.gates[t * p.gates_stride + gi + p.bw]);
         const float log_a = k * r;
         const float a = expf(log_a);
         const float m = sqrtf(-expm1f(2.0f * log_a));         // sqrt(1 - a^2) without cancellation near a = 1
@@ -296,8 +392,9 @@ struct ScanChunks {
 };
 
 __device__ __forceinline__ void recurrence_terms(const RecurrenceParams& p, size_t t, int c, float k, float& a, float& b) {
-    const float r = sigmoid_f32(p.gates[t * p.gates_stride + c]);
-    const float ig = sigmoid_f32(p.gates[t * p.gates_stride + p.W + c]);
+    const int gi = gate_index(p, c);
+    const float r = sigmoid_f32(p.gates[t * p.gates_stride + gi]);
+    const float ig = sigmoid_f32(p.gates[t * p.gates_stride + gi + p.bw]);
     const float log_a = k * r;
     a = expf(log_a);
     b = sqrtf(-expm1f(2.0f * log_a)) * ig * p.u[t * p.u_stride + c];
@@ -314,6 +411,7 @@ __global__ void recurrence_chunk_kernel(const RecurrenceParams p, const ScanChun
     const size_t slot = (size_t)ch * p.W + c, plane = (size_t)sc.n_chunks * p.W;
     if (PHASE == 1) {
         float A = 1.f, B = 0.f;
+#pragma unroll 4
         for (int li = 0; li < n; ++li) {
             float a, b;
             recurrence_terms(p, (size_t)(row0 + l0 + li), c, k, a, b);
@@ -325,6 +423,7 @@ __global__ void recurrence_chunk_kernel(const RecurrenceParams p, const ScanChun
     } else {
         float S = sc.work[2 * plane + slot];
         const float yb = p.y_bias != nullptr ? load_any(p.y_bias, p.y_bias_dt, c) : 0.f;
+#pragma unroll 4
         for (int li = 0; li < n; ++li) {
             const size_t t = (size_t)(row0 + l0 + li);
             float a, b;
@@ -354,12 +453,12 @@ RS_EXPORT int rs_gated_linear_recurrence_chunked(const float* gates, long gates_
                                                  const float* y, long y_stride, const void* y_bias, int y_bias_dt,
                                                  const void* lam, int lam_dt, void* out, int out_dt, long out_stride,
                                                  float* state, long state_stride, const int* q_start, const int* slots,
-                                                 int W, int n_seqs, float decay_c, const int* chunk_seq,
+                                                 int W, int n_seqs, float decay_c, int bw, const int* chunk_seq,
                                                  const int* chunk_start, const int* seq_first_chunk, int n_chunks,
                                                  int chunk_len, float* work, void* stream) {
     if (n_seqs <= 0 || W <= 0 || n_chunks <= 0) return 0;
     RecurrenceParams p{gates, gates_stride, u, u_stride, y, y_stride, y_bias, y_bias_dt, lam, lam_dt, out, out_dt,
-                       out_stride, state, state_stride, q_start, slots, W, n_seqs, decay_c};
+                       out_stride, state, state_stride, q_start, slots, W, n_seqs, decay_c, bw > 0 ? bw : W};
     ScanChunks sc{chunk_seq, chunk_start, seq_first_chunk, n_chunks, chunk_len, work};
     cudaStream_t s = (cudaStream_t)stream;
     const unsigned gc = (unsigned)(((long)n_chunks * W + 127) / 128), gs = (unsigned)(((long)n_seqs * W + 127) / 128);
@@ -372,11 +471,11 @@ RS_EXPORT int rs_gated_linear_recurrence_chunked(const float* gates, long gates_
 RS_EXPORT int rs_gated_linear_recurrence(const float* gates, long gates_stride, const float* u, long u_stride, const float* y,
                                          long y_stride, const void* y_bias, int y_bias_dt, const void* lam, int lam_dt,
                                          void* out, int out_dt, long out_stride, float* state, long state_stride,
-                                         const int* q_start, const int* slots, int W, int n_seqs, float decay_c,
+                                         const int* q_start, const int* slots, int W, int n_seqs, float decay_c, int bw,
                                          void* stream) {
     if (n_seqs <= 0 || W <= 0) return 0;
     RecurrenceParams p{gates, gates_stride, u, u_stride, y, y_stride, y_bias, y_bias_dt, lam, lam_dt, out, out_dt,
-                       out_stride, state, state_stride, q_start, slots, W, n_seqs, decay_c};
+                       out_stride, state, state_stride, q_start, slots, W, n_seqs, decay_c, bw > 0 ? bw : W};
     const long total = (long)n_seqs * W;
     gated_linear_recurrence_kernel<<<(unsigned)((total + 127) / 128), 128, 0, (cudaStream_t)stream>>>(p);
     return rs_launch_result();

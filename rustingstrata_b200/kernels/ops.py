@@ -118,7 +118,7 @@ def core():
                                         c_long, c_long, c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_gated_linear_recurrence.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_int,
                                                    c_void_p, c_int, c_void_p, c_int, c_long, c_void_p, c_long, c_void_p,
-                                                   c_void_p, c_int, c_int, c_float, c_void_p]
+                                                   c_void_p, c_int, c_int, c_float, c_int, c_void_p]
         lib.rs_gated_linear_recurrence_chunked.argtypes = lib.rs_gated_linear_recurrence.argtypes[:-1] + [
             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.rs_latent_kv_write.argtypes = [c_void_p, c_long, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_int, c_int,
@@ -1095,10 +1095,12 @@ def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
 
 def gated_linear_recurrence(gates: torch.Tensor, u: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor],
                             lam: torch.Tensor, out: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
-                            slots: torch.Tensor, n_seqs: int, decay: float, chunks: Optional[dict] = None) -> None:
+                            slots: torch.Tensor, n_seqs: int, decay: float, chunks: Optional[dict] = None,
+                            block_width: int = 0) -> None:
     """The real-gated linear recurrence of csrc/sequence_parts.cu over the step's packed sequences.
 
-    gates float32 [T, 2W] (pre-activations of the recurrence gate, then of the input gate), u float32 [T, W], y float32
+    gates float32 [T, 2W]: per block of ``block_width`` channels the pre-activations of the block's recurrence gate, then
+    of its input gate (0: one block, all recurrence gates, then all input gates); u float32 [T, W], y float32
     [T, W] view (pre-activation of the GELU branch), lam [W]; out [T, W]; state float32 [slots, >= W] view (updated).
 
     ``chunks``: for long portions, the step's tokens cut into chunks that run side by side (three kernels instead of one
@@ -1121,7 +1123,7 @@ def gated_linear_recurrence(gates: torch.Tensor, u: torch.Tensor, y: torch.Tenso
         raise KernelError("gated_linear_recurrence: y_bias must hold one value per channel")
     args = (_ptr(gates), gates.stride(0), _ptr(u), u.stride(0), _ptr(y), y.stride(0), _ptr(y_bias), _any_code(y_bias), _ptr(lam),
             dtype_code(lam), _ptr(out), dtype_code(out), out.stride(0), _ptr(state), state.stride(0), _ptr(q_start), _ptr(slots),
-            W, n_seqs, float(decay))
+            W, n_seqs, float(decay), int(block_width))
     if chunks is not None and chunks["n_chunks"] > 0:
         work = chunks["work"]
         if work.dtype != torch.float32 or work.numel() < 3 * chunks["n_chunks"] * W or not work.is_contiguous():

@@ -63,8 +63,9 @@ class GatedLinearRecurrence(Mixer):
         self.w_yx = torch.cat([tensors[t["y_proj"]], tensors[t["x_proj"]]], dim=0).contiguous()    # one product for both branches
         self.y_bias, self.x_bias = g("y_bias"), g("x_bias")
         self.conv_w, self.conv_bias = g("conv"), g("conv_bias")
-        self.w_r, self.b_r = g("recurrence_gate"), g("recurrence_gate_bias")
-        self.w_i, self.b_i = g("input_gate"), g("input_gate_bias")
+        # per block the recurrence gate's matrix on top of the input gate's: one block-diagonal product for both
+        self.w_gates = torch.cat([tensors[t["recurrence_gate"]], tensors[t["input_gate"]]], dim=1).contiguous()
+        self.b_gates = torch.cat([tensors[t["recurrence_gate_bias"]], tensors[t["input_gate_bias"]]], dim=1).contiguous()
         self.lam, self.w_o = g("lam"), g("o_proj")
 
     def state_need(self):
@@ -72,7 +73,7 @@ class GatedLinearRecurrence(Mixer):
 
     # Portions longer than SCAN_CHUNK tokens are cut into chunks that run side by side (the recurrence is linear in S,
     # so a chunk is a map S -> A S + B); shorter ones, and single tokens, take one thread per channel.
-    SCAN_CHUNK = 64
+    SCAN_CHUNK = 32
 
     def plan_key(self):
         return ("recurrence_chunks", self.SCAN_CHUNK)
@@ -103,10 +104,9 @@ class GatedLinearRecurrence(Mixer):
         conv_state = state[:, : max(1, self.tail)]
         ops.short_conv(yx[:, W:], self.conv_w, u, conv_state, ctx.seq_of_token, ctx.q_start, ctx.state_slots, T, ctx.n_seqs,
                        in_bias=self.x_bias, bias=self.conv_bias)
-        ops.block_linear(u, self.w_r, gates[:, :W], T, self.bw, self.bw, bias=self.b_r)
-        ops.block_linear(u, self.w_i, gates[:, W:], T, self.bw, self.bw, bias=self.b_i)
+        ops.block_linear(u, self.w_gates, gates, T, self.bw, 2 * self.bw, bias=self.b_gates)
         plan = ctx.plans[self.plan_key()]
         chunks = dict(plan, work=rt.get_scratch("rglru_scan", torch.float32).view(-1)) if plan["n_chunks"] else None
         ops.gated_linear_recurrence(gates, u, yx[:, :W], self.y_bias, self.lam, act, state[:, self.tail:], ctx.q_start,
-                                    ctx.state_slots, ctx.n_seqs, self.decay, chunks=chunks)
+                                    ctx.state_slots, ctx.n_seqs, self.decay, chunks=chunks, block_width=self.bw)
         ops.linear(act, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)
