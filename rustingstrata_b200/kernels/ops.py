@@ -1056,7 +1056,8 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, state: 
     _check(core().rs_short_conv(_ptr(x), dtype_code(x), x.stride(0), _ptr(in_bias), _any_code(in_bias), _ptr(weight),
                                 dtype_code(weight), _ptr(bias), _any_code(bias), _ptr(out), dtype_code(out), out.stride(0),
                                 _ptr(state), state.stride(0), _ptr(seq_of_token), _ptr(q_start), _ptr(slots), C, taps,
-                                1 if add_input else 0, n_tokens, n_seqs, _stream()), "short_conv", 2 if taps > 1 else 1)
+                                1 if add_input else 0, n_tokens, n_seqs, _stream()), "short_conv",
+           2 if taps > 1 and n_tokens != n_seqs else 1)
 
 
 BLOCK_LINEAR_TC_ELEMENTS = 1 << 17     # blocks of fewer weights stay on the one-launch CUDA-core kernel: a tensor-core
