@@ -44,6 +44,9 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t addr, uint32_t& r0, u
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
 
+// KS: k steps of 16 whose query fragments a warp keeps in registers across all key tiles (rows of up to 16 KS values);
+// 0: the fragments are read from shared memory at every use (any row width).
+template <int KS>
 __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lat = p.lat, pitch = lat + 8, chunks = lat >> 3;
@@ -123,6 +126,16 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
     load_tile(0, k_first);
     cp_async_commit();
     const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    uint32_t qf[KS > 0 ? KS : 1][4];
+    if (KS > 0) {
+        __syncthreads();                                       // the queries are in shared memory
+        const uint32_t qa = smem_addr(Qs + a_row * pitch + a_col);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            if (ks * 16 < lat) ldmatrix_x4(qa + ks * 32, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+            else qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
+        }
+    }
     for (int it = 0; it < n_tiles; ++it) {
         const int k0 = k_first + it * KT;
         if (it + 1 < n_tiles) {
@@ -139,11 +152,22 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
             float c[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t qa = smem_addr(Qs + a_row * pitch + a_col);
             const uint32_t kb = smem_addr(Kt + (warp * 8 + (lane & 7)) * pitch + 8 * ((lane >> 3) & 1));
-            for (int kk = 0; kk < lat; kk += 16) {
-                uint32_t a[4], b0, b1;
-                ldmatrix_x4(qa + kk * 2, a[0], a[1], a[2], a[3]);
-                ldmatrix_x2(kb + kk * 2, b0, b1);
-                mma16816(c, a, b0, b1);
+            if (KS > 0) {
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    if (ks * 16 < lat) {
+                        uint32_t b0, b1;
+                        ldmatrix_x2(kb + ks * 32, b0, b1);
+                        mma16816(c, qf[ks], b0, b1);
+                    }
+                }
+            } else {
+                for (int kk = 0; kk < lat; kk += 16) {
+                    uint32_t a[4], b0, b1;
+                    ldmatrix_x4(qa + kk * 2, a[0], a[1], a[2], a[3]);
+                    ldmatrix_x2(kb + kk * 2, b0, b1);
+                    mma16816(c, a, b0, b1);
+                }
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -331,14 +355,19 @@ RS_EXPORT int rs_attention_latent_bf16(const void* q, long q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
     if (smem > smem_allowed[dev].load(std::memory_order_acquire)) {
-        e = cudaFuncSetAttribute(latent_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(latent_attention_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(latent_attention_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         size_t seen = smem_allowed[dev].load(std::memory_order_relaxed);
         while (seen < smem && !smem_allowed[dev].compare_exchange_weak(seen, smem, std::memory_order_release)) {}
     }
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_work, (n_heads + p.hc - 1) / p.hc, decode ? max_splits : 1);
-    latent_attention_kernel<<<grid, THREADS, smem, s>>>(p);
+    // Wider rows read the query fragments from shared memory: kept in registers (20 or 36 steps) they cost a CTA 175 to
+    // 231 registers a thread, one CTA fits an SM instead of two, and the kernel got slower (593 against 431 us for 2,048
+    // tokens, 8 heads, rows of 320).
+    if (lat <= 128) latent_attention_kernel<8><<<grid, THREADS, smem, s>>>(p);
+    else latent_attention_kernel<0><<<grid, THREADS, smem, s>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess || !decode) return (int)e;
     latent_merge_kernel<<<dim3(n_work, n_heads), 128, 0, s>>>(p);
