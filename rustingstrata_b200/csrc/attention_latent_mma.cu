@@ -4,7 +4,8 @@
 // values (a 512-wide latent with a 64-wide rotated part).
 //
 // A CTA of 8 warps owns 16 query rows: (tokens of a tile) x (query heads of a chunk), all reading the same key rows.
-// Key tiles of 64 keys are streamed through two shared-memory buffers with cp.async (tile i + 1 loads under tile i).
+// Key tiles of 64 keys are streamed through two shared-memory buffers with cp.async (tile i + 1 loads under tile i), or
+// through one where two would keep a second CTA off the SM.
 // Per tile:
 //   1. S = Q K^T: warp w computes the 16 x 8 block of keys 8w .. 8w + 7 over the whole row width, scales and masks it
 //      (causal, window, the split's range) and leaves it in shared memory;
@@ -35,6 +36,7 @@ struct LatParams {
     int decode, split_keys, max_splits;
     const int* split_start; float* partial; int partial_slots;
     int* status;
+    int n_buf;                                      // key buffers in shared memory: 2 (tile i + 1 loads under tile i) or 1
 };
 
 __device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
@@ -51,8 +53,8 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lat = p.lat, pitch = lat + 8, chunks = lat >> 3;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [ROWS][pitch]
-    __nv_bfloat16* Ks = Qs + ROWS * pitch;                                          // [2][KT][pitch]
-    float* Ss = reinterpret_cast<float*>(Ks + 2 * KT * pitch);                      // [ROWS][S_PITCH]
+    __nv_bfloat16* Ks = Qs + ROWS * pitch;                                          // [n_buf][KT][pitch]
+    float* Ss = reinterpret_cast<float*>(Ks + p.n_buf * KT * pitch);                      // [ROWS][S_PITCH]
     __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + ROWS * S_PITCH);      // [ROWS][P_PITCH]
     float* stat_m = reinterpret_cast<float*>(Ps + ROWS * P_PITCH);                  // [ROWS] each
     float* stat_l = stat_m + ROWS;
@@ -138,15 +140,19 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
     }
     for (int it = 0; it < n_tiles; ++it) {
         const int k0 = k_first + it * KT;
-        if (it + 1 < n_tiles) {
+        if (p.n_buf == 2 && it + 1 < n_tiles) {
             load_tile((it + 1) & 1, k0 + KT);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
+            if (p.n_buf == 1 && it > 0) {                      // one buffer: the tile is fetched when the last one is done with
+                load_tile(0, k0);
+                cp_async_commit();
+            }
             cp_async_wait<0>();
         }
         __syncthreads();
-        const __nv_bfloat16* Kt = Ks + (size_t)(it & 1) * KT * pitch;
+        const __nv_bfloat16* Kt = Ks + (size_t)(p.n_buf == 2 ? (it & 1) : 0) * KT * pitch;
         // ---- 1. S = Q K^T for this warp's 8 keys
         {
             float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -308,10 +314,14 @@ __global__ void latent_merge_kernel(const LatParams p) {
     }
 }
 
-size_t latent_smem_bytes(int lat) {
+size_t latent_smem_bytes(int lat, int n_buf) {
     const int pitch = lat + 8;
-    return (size_t)(ROWS + 2 * KT) * pitch * 2 + (size_t)ROWS * S_PITCH * 4 + (size_t)ROWS * P_PITCH * 2 + 3 * ROWS * 4;
+    return (size_t)(ROWS + n_buf * KT) * pitch * 2 + (size_t)ROWS * S_PITCH * 4 + (size_t)ROWS * P_PITCH * 2 + 3 * ROWS * 4;
 }
+
+// Two CTAs on an SM hide more than a second key buffer does: where two buffers would leave room for one CTA only
+// (rows wider than about 380 values), the kernel runs with one buffer and the other CTA's work covers the loads.
+constexpr size_t HALF_SM_SMEM = 113 * 1024;
 
 int heads_per_cta(int n_heads, int decode) {
     if (decode || n_heads >= ROWS) return ROWS;
@@ -348,7 +358,8 @@ RS_EXPORT int rs_attention_latent_bf16(const void* q, long q_stride, void* out, 
     p.n_heads = n_heads; p.lat = lat; p.hc = heads_per_cta(n_heads, decode); p.tok_per_cta = decode ? 1 : ROWS / p.hc;
     p.window = window; p.scale = scale; p.decode = decode; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
-    const size_t smem = latent_smem_bytes(lat);
+    p.n_buf = latent_smem_bytes(lat, 2) <= HALF_SM_SMEM ? 2 : 1;
+    const size_t smem = latent_smem_bytes(lat, p.n_buf);
     static std::atomic<size_t> smem_allowed[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

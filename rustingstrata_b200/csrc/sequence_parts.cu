@@ -100,7 +100,8 @@ RS_EXPORT int rs_concat_embed(float* x, long x_stride, const void* table, int ta
 // in: [T, C] (+ in_bias[c] on every real input).  For token row t of sequence s at local index li = t - q_start[s]:
 //   out[t, c] = (add_input ? in(li) : 0) + bias[c] + sum_j w[c, j] * in(li - (taps - 1) + j),
 // in(i) for i < 0 is the sequence's state tail[taps - 1 + i] (zero after admission: nothing before the start).
-// tail: state[slot * state_stride + k * C + c], k = 0 the oldest.
+// tail: state[slot * state_stride + k * C + c], k = 0 the oldest.  w: [taps][C] (tap-major, so that neighbouring
+// channels' weights of a tap are neighbours).
 struct ConvParams {
     const void* in; int in_dt; long in_stride;
     const void* in_bias; int in_bias_dt;
@@ -131,10 +132,73 @@ __global__ void short_conv_kernel(const ConvParams p) {
     const float* tail = p.state + (size_t)p.slots[s] * p.state_stride;
     float acc = 0.f;
     for (int j = 0; j < p.taps; ++j)
-        acc = fmaf(load_any(p.w, p.w_dt, (size_t)c * p.taps + j), conv_input(p, row0, li - (p.taps - 1) + j, c, tail), acc);
+        acc = fmaf(load_any(p.w, p.w_dt, (size_t)j * p.C + c), conv_input(p, row0, li - (p.taps - 1) + j, c, tail), acc);
     if (p.bias != nullptr) acc += load_any(p.bias, p.bias_dt, c);
     if (p.add_input) acc += conv_input(p, row0, li, c, tail);
     store_any(p.out, p.out_dt, (size_t)t * p.out_stride + c, acc);
+}
+
+// eight neighbouring channels per thread with 16- or 32-byte accesses (C and the row pitches multiples of 8, aligned)
+__device__ __forceinline__ void load8(const void* p, int dt, size_t i, float* v) {
+    if (dt == RS_F32) {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { v[2 * q] = __low2float(h[q]); v[2 * q + 1] = __high2float(h[q]); }
+    }
+}
+
+__global__ void short_conv_vec_kernel(const ConvParams p) {
+    const int groups = p.C >> 3;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)p.n_tokens * groups) return;
+    const int t = (int)(idx / groups), c = (int)(idx % groups) << 3;
+    const int s = p.seq_of_token[t];
+    const int row0 = p.q_start[s];
+    const int li = t - row0;
+    const float* tail = p.state + (size_t)p.slots[s] * p.state_stride;
+    float acc[8], x[8], w[8], ib[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { acc[e] = 0.f; ib[e] = 0.f; }
+    if (p.in_bias != nullptr) load8(p.in_bias, p.in_bias_dt, c, ib);
+    for (int j = 0; j < p.taps; ++j) {
+        const int i = li - (p.taps - 1) + j;
+        if (i >= 0) {
+            load8(p.in, p.in_dt, (size_t)(row0 + i) * p.in_stride + c, x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] += ib[e];
+        } else {
+            load8(tail, RS_F32, (size_t)(p.taps - 1 + i) * p.C + c, x);
+        }
+        load8(p.w, p.w_dt, (size_t)j * p.C + c, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[e], x[e], acc[e]);
+    }
+    if (p.bias != nullptr) {
+        load8(p.bias, p.bias_dt, c, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += w[e];
+    }
+    if (p.add_input) {                                        // x still holds the current token's inputs (the last tap)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += x[e];
+    }
+    const size_t o = (size_t)t * p.out_stride + c;
+    if (p.out_dt == RS_F32) {
+        float* dst = reinterpret_cast<float*>(p.out) + o;
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+        uint4 u;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = u;
+    }
 }
 
 // the new tail: the last taps - 1 inputs of the sequence, old tail entries moving up when the step brought fewer
@@ -158,10 +222,10 @@ __global__ void short_conv_single_kernel(const ConvParams p) {
     const int row0 = p.q_start[s];
     float* tail = p.state + (size_t)p.slots[s] * p.state_stride;
     const float x = conv_input(p, row0, 0, c, tail);
-    float acc = load_any(p.w, p.w_dt, (size_t)c * p.taps + p.taps - 1) * x;
+    float acc = load_any(p.w, p.w_dt, (size_t)(p.taps - 1) * p.C + c) * x;
     for (int j = 0; j < p.taps - 1; ++j) {
         const float v = tail[(size_t)j * p.C + c];
-        acc = fmaf(load_any(p.w, p.w_dt, (size_t)c * p.taps + j), v, acc);
+        acc = fmaf(load_any(p.w, p.w_dt, (size_t)j * p.C + c), v, acc);
         if (j > 0) tail[(size_t)(j - 1) * p.C + c] = v;
     }
     if (p.taps > 1) tail[(size_t)(p.taps - 2) * p.C + c] = x;
@@ -185,7 +249,12 @@ RS_EXPORT int rs_short_conv(const void* in, int in_dt, long in_stride, const voi
         return rs_launch_result();
     }
     const long total = (long)n_tokens * C;
-    short_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(p);
+    auto aligned = [](const void* q, int dt) { return q == nullptr || ((size_t)q & (dt == RS_F32 ? 31 : 15)) == 0; };
+    const bool vec = C % 8 == 0 && in_stride % 8 == 0 && out_stride % 8 == 0 && state_stride % 8 == 0 && aligned(in, in_dt) &&
+                     aligned(out, out_dt) && aligned(w, w_dt) && aligned(bias, bias_dt) && aligned(in_bias, in_bias_dt) &&
+                     aligned(state, RS_F32);
+    if (vec) short_conv_vec_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, s>>>(p);
+    else short_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || taps == 1) return (int)e;
     const long st = (long)n_seqs * C;

@@ -1035,12 +1035,12 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, state: 
                bias: Optional[torch.Tensor] = None, add_input: bool = False) -> None:
     """Causal convolution over time on each channel for the step's packed sequences (csrc/sequence_parts.cu).
 
-    x [T, C]; weight [C, taps] (the last column multiplies the current token); out [T, C], not x itself;
+    x [T, C]; weight [taps, C] (tap-major; the last row multiplies the current token); out [T, C], not x itself;
     state: float32 [slots, >= (taps - 1) * C] view whose rows hold each request's last taps - 1 inputs (updated)."""
     _cuda(x, weight, out, state, seq_of_token, q_start, slots, in_bias, bias)
     _rows_contiguous(x, "short_conv x")
     _rows_contiguous(out, "short_conv out")
-    C, taps = weight.shape
+    taps, C = weight.shape
     if x.shape[1] < C or out.shape[1] < C or not weight.is_contiguous() or n_tokens > min(x.shape[0], out.shape[0]):
         raise KernelError(f"short_conv: x {tuple(x.shape)} / out {tuple(out.shape)} do not fit {C} channels")
     if x.data_ptr() == out.data_ptr():

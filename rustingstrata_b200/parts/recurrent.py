@@ -62,7 +62,7 @@ class GatedLinearRecurrence(Mixer):
         g = lambda k: tensors[t[k]].contiguous()                              # noqa: E731
         self.w_yx = torch.cat([tensors[t["y_proj"]], tensors[t["x_proj"]]], dim=0).contiguous()    # one product for both branches
         self.y_bias, self.x_bias = g("y_bias"), g("x_bias")
-        self.conv_w, self.conv_bias = g("conv"), g("conv_bias")
+        self.conv_w, self.conv_bias = tensors[t["conv"]].t().contiguous(), g("conv_bias")     # tap-major
         # per block the recurrence gate's matrix on top of the input gate's: one block-diagonal product for both
         self.w_gates = torch.cat([tensors[t["recurrence_gate"]], tensors[t["input_gate"]]], dim=1).contiguous()
         self.b_gates = torch.cat([tensors[t["recurrence_gate_bias"]], tensors[t["input_gate_bias"]]], dim=1).contiguous()

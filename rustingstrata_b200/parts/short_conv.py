@@ -38,7 +38,7 @@ class ShortConv(Mixer):
 
     def load(self, tensors):
         t = self.spec.tensors
-        self.weight = tensors[t["weight"]].contiguous()
+        self.weight = tensors[t["weight"]].t().contiguous()            # tap-major, as the kernel reads it
         self.bias = tensors[t["bias"]].contiguous() if self.has_bias else None
 
     def state_need(self):

@@ -368,7 +368,7 @@ def test_kernels_of_the_new_parts_against_torch():
     earlier = rn(2, C)                                                    # the second sequence's two earlier inputs
     state[0, C:] = earlier.reshape(-1).to(dev)
     oc = torch.empty(11, C, device=dev)
-    ops.short_conv(xin.to(dev), wc.to(dev), oc, state, seq_of, q_start, slots, 11, 2, add_input=True)
+    ops.short_conv(xin.to(dev), wc.t().contiguous().to(dev), oc, state, seq_of, q_start, slots, 11, 2, add_input=True)
     want0 = xin[:4] + P.causal_conv(xin[:4].double(), wc.double()).float()
     full1 = torch.cat([earlier, xin[4:]])
     want1 = (full1 + P.causal_conv(full1.double(), wc.double()).float())[2:]
