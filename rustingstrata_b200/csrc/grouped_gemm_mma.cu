@@ -14,24 +14,35 @@ namespace {
 constexpr int BM = 64, BN = 64, BK = 32, PITCH = BK + 8, THREADS = 128;
 
 struct GroupedMmaParams {
-    const __nv_bfloat16* a; long a_stride; int a_div;
+    const void* a; int a_dt; long a_stride; int a_div;             // bfloat16, or float32 rounded to bfloat16 on the way in
+    long a_expert_cols;                                            // expert e reads columns from e * a_expert_cols (0: all the same)
     const __nv_bfloat16* w; long w_expert_stride; int w_rows;      // [E][w_rows][K]
-    void* out; int out_dt; long out_stride;
-    const int* order; const int* tiles; const int* n_tiles;
+    const void* bias; int bias_dt;                                 // [E][w_rows] or null
+    void* out; int out_dt; long out_stride; long out_expert_cols;  // expert e writes columns from e * out_expert_cols
+    const int* order; const int* tiles; const int* n_tiles;        // tiles == null: every expert takes all dense_rows rows
+    int dense_rows, tiles_per_expert;
     int K, gated;
 };
 
 __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const GroupedMmaParams p) {
-    if ((int)blockIdx.y >= p.n_tiles[0]) return;
+    int e, row0, rows;
+    if (p.tiles != nullptr) {
+        if ((int)blockIdx.y >= p.n_tiles[0]) return;
+        e = p.tiles[3 * blockIdx.y]; row0 = p.tiles[3 * blockIdx.y + 1]; rows = p.tiles[3 * blockIdx.y + 2];
+    } else {
+        e = blockIdx.y / p.tiles_per_expert;
+        row0 = (blockIdx.y % p.tiles_per_expert) * BM;
+        rows = min(BM, p.dense_rows - row0);
+    }
     __shared__ __align__(16) __nv_bfloat16 As[2][BM][PITCH];
     __shared__ __align__(16) __nv_bfloat16 Ws[2][BN][PITCH];
     __shared__ int pair_of_row[BM];
-    const int e = p.tiles[3 * blockIdx.y], row0 = p.tiles[3 * blockIdx.y + 1], rows = p.tiles[3 * blockIdx.y + 2];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n0 = blockIdx.x * BN;
-    if (tid < BM) pair_of_row[tid] = tid < rows ? p.order[row0 + tid] : -1;
+    if (tid < BM) pair_of_row[tid] = tid < rows ? (p.order != nullptr ? p.order[row0 + tid] : row0 + tid) : -1;
     __syncthreads();
     const __nv_bfloat16* wbase = p.w + (size_t)e * p.w_expert_stride;
+    const size_t a_col0 = (size_t)e * p.a_expert_cols;
 
     auto load = [&](int buf, int k0) {
 #pragma unroll
@@ -40,8 +51,20 @@ __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const Grouped
             const int r = i >> 2, ch = i & 3;
             const int k = k0 + ch * 8;
             const int pr = pair_of_row[r];
-            if (pr >= 0 && k < p.K) cp_async16(smem_addr(&As[buf][r][ch * 8]), p.a + (size_t)(pr / p.a_div) * p.a_stride + k);
-            else *reinterpret_cast<uint4*>(&As[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
+            if (pr >= 0 && k < p.K) {
+                const size_t ai = (size_t)(pr / p.a_div) * p.a_stride + a_col0 + k;
+                if (p.a_dt == RS_BF16) {
+                    cp_async16(smem_addr(&As[buf][r][ch * 8]), reinterpret_cast<const __nv_bfloat16*>(p.a) + ai);
+                } else {
+                    const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.a) + ai);
+                    const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.a) + ai + 4);
+                    uint4 u;
+                    u.x = pack_bf16(lo.x, lo.y); u.y = pack_bf16(lo.z, lo.w); u.z = pack_bf16(hi.x, hi.y); u.w = pack_bf16(hi.z, hi.w);
+                    *reinterpret_cast<uint4*>(&As[buf][r][ch * 8]) = u;
+                }
+            } else {
+                *reinterpret_cast<uint4*>(&As[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
+            }
             const int gn = n0 + r;
             if (gn < p.w_rows && k < p.K) cp_async16(smem_addr(&Ws[buf][r][ch * 8]), wbase + (size_t)gn * p.K + k);
             else *reinterpret_cast<uint4*>(&Ws[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
@@ -95,16 +118,20 @@ __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const Grouped
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int gn = n0 + n_base + j * 8 + (lane & 3) * 2;
-                const float c0 = acc[i][j][2 * half], c1 = acc[i][j][2 * half + 1];
+                float c0 = acc[i][j][2 * half], c1 = acc[i][j][2 * half + 1];
+                if (p.bias != nullptr) {
+                    if (gn < p.w_rows) c0 += load_any(p.bias, p.bias_dt, (size_t)e * p.w_rows + gn);
+                    if (gn + 1 < p.w_rows) c1 += load_any(p.bias, p.bias_dt, (size_t)e * p.w_rows + gn + 1);
+                }
                 if (p.gated) {
                     if (gn + 1 < p.w_rows) {
                         const float v = silu_mul_fast(c0, c1);
-                        const size_t o = (size_t)pr * p.out_stride + (gn >> 1);
+                        const size_t o = (size_t)pr * p.out_stride + (size_t)e * p.out_expert_cols + (gn >> 1);
                         if (p.out_dt == RS_F32) reinterpret_cast<float*>(p.out)[o] = v;
                         else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
                     }
                 } else {
-                    const size_t o = (size_t)pr * p.out_stride + gn;
+                    const size_t o = (size_t)pr * p.out_stride + (size_t)e * p.out_expert_cols + gn;
                     if (p.out_dt == RS_F32) {
                         float* dst = reinterpret_cast<float*>(p.out) + o;
                         if (gn < p.w_rows) dst[0] = c0;
@@ -130,8 +157,26 @@ RS_EXPORT int rs_grouped_gemm_mma(const void* a, long a_stride, int a_div, const
     if (max_tiles <= 0 || w_rows <= 0) return 0;
     if (K <= 0 || K % 8 || a_stride % 8 || w_expert_stride % 8 || ((size_t)a & 15) || ((size_t)w & 15) || (gated && w_rows % 2))
         return (int)cudaErrorInvalidValue;
-    GroupedMmaParams p{(const __nv_bfloat16*)a, a_stride, a_div, (const __nv_bfloat16*)w, w_expert_stride, w_rows, out, out_dt,
-                       out_stride, order, tiles, n_tiles, K, gated};
+    GroupedMmaParams p{a, RS_BF16, a_stride, a_div, 0, (const __nv_bfloat16*)w, w_expert_stride, w_rows, nullptr, 0, out, out_dt,
+                       out_stride, 0, order, tiles, n_tiles, 0, 1, K, gated};
     grouped_gemm_mma_kernel<<<dim3((w_rows + BN - 1) / BN, max_tiles), THREADS, 0, (cudaStream_t)stream>>>(p);
+    return rs_launch_result();
+}
+
+// The block-diagonal product of sequence_parts.cu (rs_block_linear) for more than a few rows, through the same kernel:
+// block b is an "expert" that takes every row, reads columns from b * in_bs and writes columns from b * out_bs.
+//   out[t, b * out_bs + o] = bias[b, o] + sum_i W[b, o, i] * x[t, b * in_bs + i]
+// x: bfloat16, or float32 (rounded to bfloat16 as it enters the product); W: bfloat16 [B, O, I], I a multiple of 8.
+RS_EXPORT int rs_block_linear_mma(const void* x, int x_dt, long x_stride, long in_bs, const void* w, const void* bias,
+                                  int bias_dt, void* out, int out_dt, long out_stride, long out_bs, int T, int B, int O,
+                                  int I, void* stream) {
+    if (T <= 0 || B <= 0 || O <= 0) return 0;
+    const int align = x_dt == RS_F32 ? 4 : 8;                  // elements per 16 bytes
+    if (I <= 0 || I % 8 || x_stride % align || in_bs % align || ((size_t)x & 15) || ((size_t)w & 15))
+        return (int)cudaErrorInvalidValue;
+    const int tiles_per = (T + BM - 1) / BM;
+    GroupedMmaParams p{x, x_dt, x_stride, 1, in_bs, (const __nv_bfloat16*)w, (long)O * I, O, bias, bias_dt, out, out_dt, out_stride,
+                       out_bs, nullptr, nullptr, nullptr, T, tiles_per, I, 0};
+    grouped_gemm_mma_kernel<<<dim3((O + BN - 1) / BN, tiles_per * B), THREADS, 0, (cudaStream_t)stream>>>(p);
     return rs_launch_result();
 }

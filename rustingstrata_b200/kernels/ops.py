@@ -345,6 +345,8 @@ def bf16lib():
         lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_grouped_gemm_mma.argtypes = [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_void_p,
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rs_block_linear_mma.argtypes = [c_void_p, c_int, c_long, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_long,
+                                            c_long, c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_latent_supported.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_latent_q_per_cta.argtypes = [c_int]
         lib.rs_attention_latent_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_void_p,
@@ -1060,8 +1062,7 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, state: 
            2 if taps > 1 and n_tokens != n_seqs else 1)
 
 
-BLOCK_LINEAR_TC_ELEMENTS = 1 << 17     # blocks of fewer weights stay on the one-launch CUDA-core kernel: a tensor-core
-                                        # product per block costs about 13 us a launch whatever its size
+BLOCK_LINEAR_ROWS_FORM = 8     # up to this many rows the CUDA-core kernel's row-streaming form runs (float32 inputs stay exact)
 
 
 def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int, in_block_stride: int,
@@ -1080,14 +1081,15 @@ def block_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_row
                           f"{I} -> {O} at strides {in_block_stride}, {out_block_stride}")
     if bias is not None and (bias.numel() != B * O or not bias.is_contiguous()):
         raise KernelError("block_linear: bias must hold blocks * out values")
-    if (bias is None and n_rows > MID_MAX_ROWS and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-            and out.dtype in (torch.bfloat16, torch.float32) and I % 8 == 0 and in_block_stride % 8 == 0
-            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and (O * I) % 8 == 0
-            and O * I >= BLOCK_LINEAR_TC_ELEMENTS):
-        # a portion of a prompt: one tensor-core product per block over strided views of the same buffers
-        for b in range(B):
-            linear(x[:, b * in_block_stride: b * in_block_stride + I], weight[b],
-                   out[:, b * out_block_stride: b * out_block_stride + O], n_rows)
+    per16 = 4 if x.dtype == torch.float32 else 8
+    if (n_rows > BLOCK_LINEAR_ROWS_FORM and weight.dtype == torch.bfloat16 and x.dtype in (torch.bfloat16, torch.float32)
+            and out.dtype in (torch.bfloat16, torch.float32) and I % 8 == 0 and in_block_stride % per16 == 0
+            and x.stride(0) % per16 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        # more than a few rows, bfloat16 weights: the tensor-core kernel of the grouped product, a block as an "expert"
+        # that takes every row (float32 inputs are rounded to bfloat16 as they enter the product)
+        _check(bf16lib().rs_block_linear_mma(_ptr(x), dtype_code(x), x.stride(0), in_block_stride, _ptr(weight), _ptr(bias),
+                                             _any_code(bias), _ptr(out), dtype_code(out), out.stride(0), out_block_stride,
+                                             n_rows, B, O, I, _stream()), "block_linear_mma")
         return
     _check(core().rs_block_linear(_ptr(x), dtype_code(x), x.stride(0), in_block_stride, _ptr(weight), dtype_code(weight),
                                   _ptr(bias), _any_code(bias), _ptr(out), dtype_code(out), out.stride(0), out_block_stride,
