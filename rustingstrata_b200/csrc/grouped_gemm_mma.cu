@@ -1,17 +1,17 @@
 // One launch for the products of all experts of a mixture, on the warp-level tensor cores (mma.sync m16n8k16,
 // bfloat16 operands, float32 accumulation): the bfloat16 engine's form of the grouped product in moe_simt.cu, with
-// the same work list (moe_route: the step's (token, k) pairs sorted by expert and cut into row tiles of 64).
+// the same work list (moe_route: the step's (token, k) pairs sorted by expert and cut into row tiles of 64 or 128).
 //
-// A CTA of 4 warps takes one row tile of one expert and 64 rows of the expert's matrix; it gathers its input rows
-// through the sorted list (pair p reads row p / a_div of A), streams A and W in steps of 32 of k through two
-// shared-memory buffers with cp.async, and writes every pair's result to the pair's own row of the output.  A warp owns
-// 32 x 32 of the tile.  Epilogues: plain store (float32 or bfloat16), or SiLU(gate) * up for a matrix whose rows
+// A CTA takes one row tile of one expert and a tile of rows of the expert's matrix (64 x 64 with 4 warps, or 128 x 128
+// with 8); it gathers its input rows through the sorted list (pair p reads row p / a_div of A), streams A and W in steps
+// of 32 of k through two shared-memory buffers with cp.async, and writes every pair's result to the pair's own row of the
+// output.  Epilogues: plain store (float32 or bfloat16), or SiLU(gate) * up for a matrix whose rows
 // alternate gate, up: the two lie in neighbouring accumulator columns of one thread, and the output has half the columns.
 // Every output element accumulates k in ascending order, whatever else is in the batch.
 #include "mma_helpers.cuh"
 
 namespace {
-constexpr int BM = 64, BN = 64, BK = 32, PITCH = BK + 8, THREADS = 128;
+constexpr int BK = 32, PITCH = BK + 8;
 
 struct GroupedMmaParams {
     const void* a; int a_dt; long a_stride; int a_div;             // bfloat16, or float32 rounded to bfloat16 on the way in
@@ -24,7 +24,12 @@ struct GroupedMmaParams {
     int K, gated;
 };
 
-__global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const GroupedMmaParams p) {
+// BM x BN: the CTA's tile; WM x WN warps, each owning (BM / WM) x (BN / WN) of it.  64 x 64 with 2 x 2 warps where an
+// expert has few rows (a decode step reads every expert's matrix for a handful of rows: the weights are the cost), 128 x
+// 128 with 2 x 4 warps for prompt portions, where the traffic from L2 per multiply-add halves with the tile's edge.
+template <int BM, int BN, int WM, int WN>
+__global__ void __launch_bounds__(WM * WN * 32) grouped_gemm_mma_kernel(const GroupedMmaParams p) {
+    constexpr int THREADS = WM * WN * 32, MT = BM / WM / 16, NT = BN / WN / 8;
     int e, row0, rows;
     if (p.tiles != nullptr) {
         if ((int)blockIdx.y >= p.n_tiles[0]) return;
@@ -46,8 +51,8 @@ __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const Grouped
 
     auto load = [&](int buf, int k0) {
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int i = tid + q * THREADS;               // 256 chunks of 16 bytes per operand tile
+        for (int q = 0; q < BM * 4 / THREADS; ++q) {
+            const int i = tid + q * THREADS;               // BM * 4 chunks of 16 bytes
             const int r = i >> 2, ch = i & 3;
             const int k = k0 + ch * 8;
             const int pr = pair_of_row[r];
@@ -65,18 +70,24 @@ __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const Grouped
             } else {
                 *reinterpret_cast<uint4*>(&As[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
             }
+        }
+#pragma unroll
+        for (int q = 0; q < BN * 4 / THREADS; ++q) {
+            const int i = tid + q * THREADS;
+            const int r = i >> 2, ch = i & 3;
+            const int k = k0 + ch * 8;
             const int gn = n0 + r;
             if (gn < p.w_rows && k < p.K) cp_async16(smem_addr(&Ws[buf][r][ch * 8]), wbase + (size_t)gn * p.K + k);
             else *reinterpret_cast<uint4*>(&Ws[buf][r][ch * 8]) = make_uint4(0, 0, 0, 0);
         }
     };
 
-    float acc[2][4][4];
+    float acc[MT][NT][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f; }
-    const int m_base = (warp >> 1) * 32, n_base = (warp & 1) * 32;
+        for (int j = 0; j < NT; ++j) { acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f; }
+    const int m_base = (warp / WN) * (BM / WM), n_base = (warp % WN) * (BN / WN);
     const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
     const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
     const int n_steps = (p.K + BK - 1) / BK;
@@ -94,29 +105,29 @@ __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const Grouped
         const int buf = s & 1;
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 16) {
-            uint32_t a[2][4], b[4][2];
+            uint32_t a[MT][4], b[NT][2];
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < MT; ++i)
                 ldmatrix_x4(smem_addr(&As[buf][m_base + i * 16 + a_row][kk + a_col]), a[i][0], a[i][1], a[i][2], a[i][3]);
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+            for (int j = 0; j < NT / 2; ++j)
                 ldmatrix_x4(smem_addr(&Ws[buf][n_base + j * 16 + b_row][kk + b_col]), b[2 * j][0], b[2 * j][1], b[2 * j + 1][0],
                             b[2 * j + 1][1]);
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < MT; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) mma16816(acc[i][j], a[i], b[j][0], b[j][1]);
+                for (int j = 0; j < NT; ++j) mma16816(acc[i][j], a[i], b[j][0], b[j][1]);
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MT; ++i)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int pr = pair_of_row[m_base + i * 16 + (lane >> 2) + 8 * half];
             if (pr < 0) continue;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < NT; ++j) {
                 const int gn = n0 + n_base + j * 8 + (lane & 3) * 2;
                 float c0 = acc[i][j][2 * half], c1 = acc[i][j][2 * half + 1];
                 if (p.bias != nullptr) {
@@ -147,19 +158,21 @@ __global__ void __launch_bounds__(THREADS) grouped_gemm_mma_kernel(const Grouped
 }
 }  // namespace
 
-RS_EXPORT int rs_grouped_gemm_mma_rows_per_tile() { return BM; }
+// Rows of one expert per CTA: the tile for few rows per expert (large == 0) and the one for prompt portions.
+RS_EXPORT int rs_grouped_gemm_mma_rows_per_tile(int large) { return large ? 128 : 64; }
 
 // a: bfloat16 [*, K] rows 16-byte aligned; w: bfloat16 [E][w_rows][K]; out: [pairs, w_rows] (or w_rows / 2 when gated,
 // the rows of w alternating gate, up).  K a multiple of 8.
 RS_EXPORT int rs_grouped_gemm_mma(const void* a, long a_stride, int a_div, const void* w, long w_expert_stride, int w_rows,
                                   void* out, int out_dt, long out_stride, const int* order, const int* tiles,
-                                  const int* n_tiles, int max_tiles, int K, int gated, void* stream) {
+                                  const int* n_tiles, int max_tiles, int K, int gated, int large, void* stream) {
     if (max_tiles <= 0 || w_rows <= 0) return 0;
     if (K <= 0 || K % 8 || a_stride % 8 || w_expert_stride % 8 || ((size_t)a & 15) || ((size_t)w & 15) || (gated && w_rows % 2))
         return (int)cudaErrorInvalidValue;
     GroupedMmaParams p{a, RS_BF16, a_stride, a_div, 0, (const __nv_bfloat16*)w, w_expert_stride, w_rows, nullptr, 0, out, out_dt,
                        out_stride, 0, order, tiles, n_tiles, 0, 1, K, gated};
-    grouped_gemm_mma_kernel<<<dim3((w_rows + BN - 1) / BN, max_tiles), THREADS, 0, (cudaStream_t)stream>>>(p);
+    if (large) grouped_gemm_mma_kernel<128, 128, 2, 4><<<dim3((w_rows + 127) / 128, max_tiles), 256, 0, (cudaStream_t)stream>>>(p);
+    else grouped_gemm_mma_kernel<64, 64, 2, 2><<<dim3((w_rows + 63) / 64, max_tiles), 128, 0, (cudaStream_t)stream>>>(p);
     return rs_launch_result();
 }
 
@@ -174,9 +187,11 @@ RS_EXPORT int rs_block_linear_mma(const void* x, int x_dt, long x_stride, long i
     const int align = x_dt == RS_F32 ? 4 : 8;                  // elements per 16 bytes
     if (I <= 0 || I % 8 || x_stride % align || in_bs % align || ((size_t)x & 15) || ((size_t)w & 15))
         return (int)cudaErrorInvalidValue;
-    const int tiles_per = (T + BM - 1) / BM;
+    const int bm = T > 256 ? 128 : 64;
+    const int tiles_per = (T + bm - 1) / bm;
     GroupedMmaParams p{x, x_dt, x_stride, 1, in_bs, (const __nv_bfloat16*)w, (long)O * I, O, bias, bias_dt, out, out_dt, out_stride,
                        out_bs, nullptr, nullptr, nullptr, T, tiles_per, I, 0};
-    grouped_gemm_mma_kernel<<<dim3((O + BN - 1) / BN, tiles_per * B), THREADS, 0, (cudaStream_t)stream>>>(p);
+    if (bm == 128) grouped_gemm_mma_kernel<128, 128, 2, 4><<<dim3((O + 127) / 128, tiles_per * B), 256, 0, (cudaStream_t)stream>>>(p);
+    else grouped_gemm_mma_kernel<64, 64, 2, 2><<<dim3((O + 63) / 64, tiles_per * B), 128, 0, (cudaStream_t)stream>>>(p);
     return rs_launch_result();
 }

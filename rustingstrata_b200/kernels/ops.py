@@ -344,7 +344,8 @@ def bf16lib():
         lib.rs_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_grouped_gemm_mma.argtypes = [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_void_p,
-                                            c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rs_grouped_gemm_mma_rows_per_tile.argtypes = [c_int]
         lib.rs_block_linear_mma.argtypes = [c_void_p, c_int, c_long, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_long,
                                             c_long, c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_latent_supported.argtypes = [c_int, c_int, c_int]
@@ -1209,7 +1210,7 @@ def moe_route(ids: torch.Tensor, table: torch.Tensor, n_experts: int, n_tokens: 
             raise KernelError(f"moe_route: {name} must be contiguous int32")
     if order.numel() < n_tokens * top or ids.numel() < n_tokens:
         raise KernelError("moe_route: order must hold tokens * top entries")
-    if rows_per_tile not in (grouped_rows_per_tile(True), grouped_rows_per_tile(False)):
+    if rows_per_tile not in (grouped_rows_per_tile(True), grouped_rows_per_tile(False), GROUPED_ROWS_LARGE):
         raise KernelError("moe_route: rows_per_tile must be a tile size of the grouped product")
     _check(core().rs_moe_route(_ptr(ids), _ptr(table), V, top, n_experts, n_tokens, rows_per_tile, _ptr(order), _ptr(tiles),
                                _ptr(n_tiles), tiles.numel() // 3, _ptr(status), _stream()), "moe_route")
@@ -1244,11 +1245,15 @@ def grouped_gemm_mma_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
             and weight.data_ptr() % 16 == 0)
 
 
+GROUPED_ROWS_LARGE = 128      # row tile of the tensor-core grouped product's form for prompt portions
+
+
 def grouped_gemm_mma(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch.Tensor, order: torch.Tensor,
-                     tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool) -> None:
+                     tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, large: bool = False) -> None:
     """The grouped product of :func:`grouped_linear` on the tensor cores (csrc/grouped_gemm_mma.cu), for the row tiles
-    of ``GROUPED_ROWS_TILED`` that ``moe_route`` lists.  ``gated``: the rows of every expert's matrix alternate gate, up
-    and out = SiLU(gate) * up has half as many columns as the matrix has rows."""
+    that ``moe_route`` lists: of ``GROUPED_ROWS_TILED`` rows (64 x 64 tiles, for few rows per expert), or with ``large`` of
+    ``GROUPED_ROWS_LARGE`` (128 x 128 tiles, for prompt portions).  ``gated``: the rows of every expert's matrix alternate
+    gate, up and out = SiLU(gate) * up has half as many columns as the matrix has rows."""
     _cuda(a, weight, out, order, tiles, n_tiles)
     _rows_contiguous(out, "grouped_gemm_mma out")
     if not grouped_gemm_mma_ok(a, weight):
@@ -1257,11 +1262,12 @@ def grouped_gemm_mma(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: tor
     if a.shape[1] != K or out.shape[1] != (rows // 2 if gated else rows) or (gated and rows % 2) or max_tiles * 3 > tiles.numel():
         raise KernelError(f"grouped_gemm_mma: a {tuple(a.shape)} x weight {tuple(weight.shape)} -> out {tuple(out.shape)} "
                           f"does not fit")
-    if int(bf16lib().rs_grouped_gemm_mma_rows_per_tile()) != GROUPED_ROWS_TILED:
-        raise KernelError("grouped_gemm_mma: the compiled kernel's row tile differs from the launcher's")
+    if (int(bf16lib().rs_grouped_gemm_mma_rows_per_tile(0)), int(bf16lib().rs_grouped_gemm_mma_rows_per_tile(1))) != \
+            (GROUPED_ROWS_TILED, GROUPED_ROWS_LARGE):
+        raise KernelError("grouped_gemm_mma: the compiled kernel's row tiles differ from the launcher's")
     _check(bf16lib().rs_grouped_gemm_mma(_ptr(a), a.stride(0), a_div, _ptr(weight), weight.stride(0), rows, _ptr(out),
                                          dtype_code(out), out.stride(0), _ptr(order), _ptr(tiles), _ptr(n_tiles), max_tiles,
-                                         K, 1 if gated else 0, _stream()), "grouped_gemm_mma")
+                                         K, 1 if gated else 0, 1 if large else 0, _stream()), "grouped_gemm_mma")
 
 
 def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tensor, n_tokens: int,

@@ -54,6 +54,7 @@ class TableMoE(FeedForward):
     tensors: table [vocab, top]; expert_gate / expert_up / expert_down: name patterns with ``{e}`` for the expert's
     number; shared_gate, shared_up, shared_down, shared_scale [1, hidden] when there is a shared expert."""
     SMALL_PAIRS_PER_EXPERT = 4      # up to this many (token, k) pairs per expert on average the row-streaming form runs
+    LARGE_PAIRS_PER_EXPERT = 96     # from this many on average the tensor-core product takes its 128 x 128 tiles
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -71,17 +72,15 @@ class TableMoE(FeedForward):
         rt.scratch(self.act_name, pairs, self.ff)
         rt.scratch("moe_pair_out", pairs, self.hidden, torch.float32)
         rt.scratch("moe_order", 1, pairs, torch.int32)
-        self.max_tiles_small = self._max_tiles(pairs, True)
-        rt.scratch("moe_tiles", 1, 3 * max(self.max_tiles_small, self._max_tiles(pairs, False)) + 4, torch.int32)
+        rt.scratch("moe_tiles", 1, 3 * self._max_tiles(pairs, min(_ROWS_PER_TILE.values())) + 4, torch.int32)
         rt.scratch("moe_delta", rt.max_batch_tokens, self.hidden, torch.float32)
         if self.shared_ff:
             rt.scratch("moe_shared_act", rt.max_batch_tokens, self.shared_ff)
             rt.scratch("moe_shared_gu", rt.max_batch_tokens, 2 * self.shared_ff)
             rt.scratch("moe_shared_out", rt.max_batch_tokens, self.hidden, torch.float32)
 
-    def _max_tiles(self, pairs: int, small: bool) -> int:
-        """Row tiles the grouped product can meet: full tiles, plus at most one partly filled per expert in use."""
-        rows = _ROWS_PER_TILE[small]
+    def _max_tiles(self, pairs: int, rows: int) -> int:
+        """Row tiles of ``rows`` the grouped product can meet: full tiles, plus at most one partly filled per expert in use."""
         return pairs // rows + min(self.n_experts, pairs)
 
     def tensor_needs(self):
@@ -132,16 +131,18 @@ class TableMoE(FeedForward):
         # bfloat16 engine: one tensor-core launch per projection for all experts, whatever the step's size
         tensor_cores = self.interleaved
         small = not tensor_cores and pairs <= self.SMALL_PAIRS_PER_EXPERT * self.n_experts
-        max_tiles = self._max_tiles(pairs, small)
+        large = tensor_cores and pairs >= self.LARGE_PAIRS_PER_EXPERT * self.n_experts
+        rows = ops.GROUPED_ROWS_LARGE if large else _ROWS_PER_TILE[small]
+        max_tiles = self._max_tiles(pairs, rows)
         order = rt.get_scratch("moe_order", torch.int32).view(-1)
         tiles = rt.get_scratch("moe_tiles", torch.int32).view(-1)
         n_tiles, tiles = tiles[:1], tiles[4:]
         act = rt.get_scratch(self.act_name)[:, : self.ff]
         pair_out = rt.get_scratch("moe_pair_out", torch.float32)[:, : self.hidden]
-        ops.moe_route(ctx.token_ids, self.table, self.n_experts, T, _ROWS_PER_TILE[small], order, tiles, n_tiles, ctx.status)
+        ops.moe_route(ctx.token_ids, self.table, self.n_experts, T, rows, order, tiles, n_tiles, ctx.status)
         if tensor_cores:
-            ops.grouped_gemm_mma(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True)
-            ops.grouped_gemm_mma(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False)
+            ops.grouped_gemm_mma(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True, large=large)
+            ops.grouped_gemm_mma(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, large=large)
         else:
             ops.grouped_linear(h, top, self.w_gate_up, act, order, tiles, n_tiles, max_tiles, gated=True, small=small)
             ops.grouped_linear(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, small=small)
