@@ -367,7 +367,7 @@ def lokinex_config(width: int) -> dict:
     (attention + dense, recurrence + experts, attention + experts, recurrence + experts) run twice by the loop."""
     heads = width // 128
     att = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": width // 4,
-                                                 "rot": {"base": 250000.0, "dims": 64}, "scale": 128 ** -0.5}}
+                                                 "rot": {"base": 1000000.0, "dims": 64}, "scale": 128 ** -0.5}}
     rec = {"type": "rglru", "mixer": {"width": width * 5 // 4, "blocks": width * 5 // 4 // 256, "conv": 4}}
     moe = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": width * 3 // 4}, "shared": {"ff": width * 3 // 2}}
     dense = {"kind": "dense", "ff": 4 * width}

@@ -63,7 +63,7 @@ CONFIGS = {
     ], eps=1e-5),
     # wider, one pass of a loop over everything, long taps, for long sequences
     "R": config(320, 256, [
-        (latent(4, 32, 32, 48, 96, base=250000.0), moe(8, 2, 64, shared=96)),
+        (latent(4, 32, 32, 48, 96, base=100000.0), moe(8, 2, 64, shared=96)),
         (rglru(192, 2, 5), dense(384)),
     ], eps=1e-5, canon=4, loop=(0, 2, 1)),
 }

@@ -377,7 +377,7 @@ def test_kernels_of_the_new_parts_against_torch():
     assert torch.allclose(state[0].cpu().reshape(taps - 1, C), xin[8:11], atol=0)
 
 
-@pytest.mark.parametrize("heads,lat,page", [(6, 80, 16), (16, 576, 16), (3, 48, 8), (20, 128, 32), (1, 16, 4)])
+@pytest.mark.parametrize("heads,lat,page", [(7, 96, 16), (16, 576, 16), (3, 48, 8), (20, 128, 32), (1, 16, 4)])
 def test_tensor_core_latent_attention_against_torch(heads, lat, page):
     """The tensor-core kernel of latent attention (portions and the split form) against a plain float32 computation on
     the same bfloat16 inputs: sequences of unequal length, portions that start in the middle of a page, single tokens
