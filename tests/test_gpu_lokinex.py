@@ -213,7 +213,7 @@ def test_sharp_weights_look_far_back_and_keep_state(tmp_path_factory):
     toks = tokens_for(cfg, 700, 77)
     full = plain_logits(cfg, w, toks)[-20:]
     cut = plain_logits(cfg, w, toks[100:])[-20:]
-    assert np.max(np.abs(full - cut)) / np.max(np.abs(full)) > 5 * TOL_SHARP["bfloat16"]
+    assert np.max(np.abs(full - cut)) / np.max(np.abs(full)) > 3 * TOL_SHARP["bfloat16"]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
