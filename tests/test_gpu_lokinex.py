@@ -253,6 +253,32 @@ def test_long_decoding(tmp_path_factory, dtype):
     assert err.max() <= TOL_SHARP[dtype], f"first wrong position {int(np.argmax(err > TOL_SHARP[dtype]))}"
 
 
+WIDE = {
+    # rows of 384 and 544 values in the latent cache, 20 heads (two chunks of a CTA's rows), a prompt long enough for the
+    # 128 x 128 tiles of the grouped product and of the block-diagonal product
+    "wide_latent": M.config(500, 512, [(M.latent(20, 32, 64, 48, 320, base=1e5), M.moe(4, 2, 256, shared=128)),
+                                        (M.rglru(768, 3, 4), M.dense(1024)),
+                                        (M.latent(5, 64, 32, 64, 512, rot_dims=16), M.moe(6, 3, 64))], eps=1e-5, canon=4, loop=(0, 2, 2)),
+    # more experts than a portion has tokens per expert, beside a layer whose three experts each see a third of the prompt
+    "many_experts": M.config(300, 256, [(M.rglru(256, 1, 3), M.moe(40, 4, 128, shared=256)),
+                                         (M.latent(4, 64, 64, 128, 64), M.moe(3, 1, 512))], canon=2),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(WIDE))
+def test_wider_shapes_and_long_portions(tmp_path_factory, name, dtype):
+    """A portion of 700 tokens, 40 single tokens, a portion of 160: the forms of the kernels that only large steps and
+    wide rows reach."""
+    path, cfg, w = model(tmp_path_factory, "wide_" + name, WIDE[name], seed=7)
+    toks = tokens_for(cfg, 900, 3)
+    ref = plain_logits(cfg, w, toks)
+    r = runner_for(path, dtype, page_size=16, pool_tokens=1024, max_batch_tokens=1024)
+    got = [step_all(r, "a", toks[:700])] + [step_all(r, "a", [t]) for t in toks[700:740]] + [step_all(r, "a", toks[740:])]
+    err = np.max(np.abs(np.concatenate(got) - ref), axis=1) / np.max(np.abs(ref))
+    assert err.max() <= TOL[dtype], f"first wrong position {int(np.argmax(err > TOL[dtype]))}"
+
+
 # ----------------------------------------------------------------------------- the engine's own entry points
 @pytest.mark.parametrize("chunk", [None, 7])
 def test_greedy_generation_through_the_scheduler(tmp_path_factory, chunk):
