@@ -71,4 +71,14 @@ def load_model_config(model_dir: str):
     """(architecture, typed configuration) of a model folder."""
     raw = read_config_json(model_dir)
     arch = resolve_architecture(raw, where=f"{model_dir}/config.json")
-    return arch, arch.config_class.from_dict(raw, where=f"{model_dir}/config.json")
+    config = arch.config_class.from_dict(raw, where=f"{model_dir}/config.json")
+    if hasattr(config, "resolve_shapes"):
+        # sizes that an architecture leaves to its tensors' shapes (the rows of a table, say)
+        from ..weights.safetensors_io import SafetensorsError, index_model_dir
+        try:
+            shapes = {name: tuple(e.shape) for name, e in index_model_dir(model_dir).items()}
+        except SafetensorsError:
+            shapes = None                          # a folder with a configuration only
+        if shapes is not None:
+            config = config.resolve_shapes(shapes)
+    return arch, config

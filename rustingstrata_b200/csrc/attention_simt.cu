@@ -40,6 +40,7 @@ struct AttnParams {
     int window;                            // 0 = all keys
     float scale;
     const float* slopes;                   // [n_q] or null: slopes[h] * (key position - query position) is added to a score
+    const float* dist_bias; int n_dist;    // [n_dist][n_q] or null: dist_bias[min(query - key position, n_dist - 1)][h] is added
     int decode, split_keys, max_splits;
     const int* split_start;                // decode: [n_work] first partial slot of each sequence
     float* partial;                        // decode: [slot][n_q][hd + 2], slot = split_start[w] + split
@@ -133,6 +134,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(const AttnP
             for (int d = 0; d < hd; ++d) s = fmaf(qr[d], kr[d], s);
             s *= p.scale;
             if (p.slopes != nullptr) s = fmaf(p.slopes[head0 + r % n_heads], (float)(kpos - qpos), s);   // a bias linear in the distance
+            if (p.dist_bias != nullptr)                                                                 // a bias tabulated by distance
+                s += p.dist_bias[(size_t)min(max(qpos - kpos, 0), p.n_dist - 1) * p.n_q + head0 + r % n_heads];
             const bool ok = kpos >= key_lo && kpos < key_hi && kpos <= qpos &&
                             (p.window <= 0 || kpos > qpos - p.window);
             s = ok ? s : -INFINITY;
@@ -262,8 +265,10 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
                                 int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
                                 int n_q, int n_kv, int hd, int window, float scale, int decode, int split_keys,
                                 int max_splits, const int* split_start, float* partial, int partial_slots,
-                                const float* slopes, int one_plane, int* status, void* stream) {
+                                const float* slopes, const float* dist_bias, int n_dist, int one_plane, int* status,
+                                void* stream) {
     if (n_work <= 0) return 0;
+    if (dist_bias != nullptr && n_dist <= 0) return (int)cudaErrorInvalidValue;
     if (hd % 16 || hd > 576 || hd <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
     if (decode && (split_keys % KT || split_keys <= 0 || max_splits <= 0 || partial == nullptr || partial_slots <= 0 ||
                    split_start == nullptr))
@@ -278,7 +283,7 @@ RS_EXPORT int rs_attention_simt(const void* q, long q_stride, void* out, long ou
     p.q_per_cta = decode ? 1 : ROWS / p.heads_per_cta;
     p.window = window; p.scale = scale; p.decode = decode; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
-    p.slopes = slopes;
+    p.slopes = slopes; p.dist_bias = dist_bias; p.n_dist = n_dist;
     p.v_offset = one_plane ? 0 : (long)n_kv * page_size * hd;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RS_F32) return dispatch_hd<float, true>(p, n_work, s);
@@ -366,7 +371,7 @@ RS_EXPORT int rs_attention_decode_noalloc(const void* q, long q_stride, void* ou
     p.chunks_per_group = (p.group + p.heads_per_cta - 1) / p.heads_per_cta;
     p.q_per_cta = 1;
     p.window = window; p.scale = scale; p.decode = 1; p.split_keys = split_keys; p.max_splits = max_splits;
-    p.split_start = split_start; p.partial = partial; p.status = status; p.slopes = nullptr;
+    p.split_start = split_start; p.partial = partial; p.status = status; p.slopes = nullptr; p.dist_bias = nullptr; p.n_dist = 0;
     p.v_offset = (long)n_kv * page_size * hd;
     // what the array really holds for this shape, not what the caller said it would use: a split list that
     // disagrees with total_splits is flagged by the kernels (RS_STATUS_BAD_PLAN) instead of written past the array

@@ -1,0 +1,161 @@
+// What surrounds attention whose queries, keys and values pass a short convolution over time, for both engines:
+//   * conv_norm_kv_write: per channel of the projected [q | k | v] rows a causal convolution over time (the last
+//     taps - 1 projected rows of every request come from its state slot), q and k heads divided by their root mean
+//     square, q stored head by head in rows padded to the attention kernels' head size, k and v written into the
+//     request's cache pages (padding zero);
+//   * conv_tail_update: the state slot's last taps - 1 projected rows after the step;
+//   * sigmoid_gate: joined heads times sigmoid(gate), out of the padded rows.
+// The convolution, the norms and the sigmoid are float32; a (token, head) is a warp's, so its sums have one order.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int MAX_PER_LANE = 8;          // head sizes up to 256
+
+__device__ __forceinline__ void store_any(void* p, int dt, size_t i, float v) {
+    if (dt == RS_F32) reinterpret_cast<float*>(p)[i] = v;
+    else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+struct ConvKvParams {
+    const void* proj; int dt; long proj_stride;       // [T, >= C] projected rows: q heads, then k heads, then v heads
+    const void* w; int w_dt;                          // [taps, C] tap-major; null with taps == 0: no convolution
+    const float* tail; long tail_stride;              // [slots, (taps - 1) * C]
+    int C, taps;
+    int n_q, n_kv, dk, dv, hdp;                       // head counts, key and value sizes, padded head size
+    int unit_norm; float eps;
+    void* q_out; long q_stride;                       // [T, n_q * hdp]
+    void* cache; long page_stride; long v_offset;     // [pages][2][n_kv][page_size][hdp]
+    int num_pages, page_size, write_kv;
+    const int* block_table; int table_stride;
+    const int* positions; int pos_stride; const int* seq_of_token; const int* q_start; const int* slots;
+    int n_tokens;
+    int* status;
+};
+
+__global__ void __launch_bounds__(128) conv_norm_kv_write_kernel(const ConvKvParams p) {
+    const int lane = threadIdx.x & 31;
+    const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
+    const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long)p.n_tokens * items) return;
+    const int t = (int)(wid / items), item = (int)(wid % items);
+    const int s = p.seq_of_token[t];
+    const int row0 = p.q_start[s], li = t - row0;
+    const float* tail = p.tail + (size_t)p.slots[s] * p.tail_stride;
+    int base, width, kind;                             // kind 0 q, 1 k, 2 v
+    if (item < p.n_q) { kind = 0; base = item * p.dk; width = p.dk; }
+    else if (item < p.n_q + p.n_kv) { kind = 1; base = p.n_q * p.dk + (item - p.n_q) * p.dk; width = p.dk; }
+    else { kind = 2; base = (p.n_q + p.n_kv) * p.dk + (item - p.n_q - p.n_kv) * p.dv; width = p.dv; }
+    float acc[MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        acc[i] = 0.f;
+        if (d >= width) continue;
+        const int c = base + d;
+        float a = 0.f;
+        if (p.taps <= 0) {
+            a = load_any(p.proj, p.dt, (size_t)t * p.proj_stride + c);
+        } else {
+            for (int j = 0; j < p.taps; ++j) {
+                const int src = li - (p.taps - 1) + j;
+                const float x = src >= 0 ? load_any(p.proj, p.dt, (size_t)(row0 + src) * p.proj_stride + c)
+                                         : tail[(size_t)(p.taps - 1 + src) * p.C + c];
+                a = fmaf(load_any(p.w, p.w_dt, (size_t)j * p.C + c), x, a);
+            }
+        }
+        acc[i] = a;
+        ss = fmaf(a, a, ss);
+    }
+    float r = 1.0f;
+    if (p.unit_norm && kind != 2) {
+        ss = warp_sum(ss);
+        r = 1.0f / sqrtf(ss / (float)width + p.eps);
+    }
+    void* dst; size_t o;
+    if (kind == 0) {
+        dst = p.q_out; o = (size_t)t * p.q_stride + (size_t)item * p.hdp;
+    } else {
+        const int pos = p.positions[(size_t)t * p.pos_stride];
+        const int page = p.block_table[(size_t)s * p.table_stride + pos / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+            if (lane == 0) atomicOr(p.status, RS_STATUS_BAD_PAGE);
+            return;
+        }
+        const int g = kind == 1 ? item - p.n_q : item - p.n_q - p.n_kv;
+        dst = p.cache;
+        o = (size_t)page * p.page_stride + ((size_t)g * p.page_size + pos % p.page_size) * p.hdp + (kind == 2 ? p.v_offset : 0);
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < p.hdp) store_any(dst, p.dt, o + d, d < width ? acc[i] * r : 0.f);
+    }
+}
+
+// tail[i] <- the projected row at local index q_len - (taps - 1) + i: a row of this step, or a row the tail held.
+// One thread per (sequence, channel), i ascending: a row read from the tail lies behind the one being written.
+__global__ void conv_tail_update_kernel(const void* __restrict__ proj, int dt, long proj_stride, float* __restrict__ tails,
+                                        long tail_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
+                                        int C, int taps, int n_seqs) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_seqs * C) return;
+    const int s = (int)(idx / C), c = (int)(idx % C);
+    const int row0 = q_start[s], q_len = q_start[s + 1] - row0;
+    float* tail = tails + (size_t)slots[s] * tail_stride;
+    for (int i = 0; i < taps - 1; ++i) {
+        const int src = q_len - (taps - 1) + i;
+        tail[(size_t)i * C + c] = src >= 0 ? load_any(proj, dt, (size_t)(row0 + src) * proj_stride + c)
+                                           : tail[(size_t)(taps - 1 + src) * C + c];
+    }
+}
+
+// out[t, h * dv + d] = a[t, h * hdp + d] * sigmoid(g[t, h * dv + d])    (g == null: a copy out of the padded rows)
+__global__ void sigmoid_gate_kernel(const void* __restrict__ a, long a_stride, const void* __restrict__ g, long g_stride,
+                                    void* __restrict__ out, long out_stride, int dt, int n_heads, int dv, int hdp,
+                                    int n_tokens) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int W = n_heads * dv;
+    if (idx >= (long)n_tokens * W) return;
+    const int t = (int)(idx / W), c = (int)(idx % W);
+    const int h = c / dv, d = c % dv;
+    float v = load_any(a, dt, (size_t)t * a_stride + (size_t)h * hdp + d);
+    if (g != nullptr) v *= 1.0f / (1.0f + expf(-load_any(g, dt, (size_t)t * g_stride + c)));
+    store_any(out, dt, (size_t)t * out_stride + c, v);
+}
+}  // namespace
+
+RS_EXPORT int rs_conv_norm_kv_write(const void* proj, int dt, long proj_stride, const void* w, int w_dt, float* tails,
+                                    long tail_stride, int C, int taps, int n_q, int n_kv, int dk, int dv, int hdp,
+                                    int unit_norm, float eps, void* q_out, long q_stride, void* cache, long page_stride,
+                                    int num_pages, int page_size, int write_kv, const int* block_table, int table_stride,
+                                    const int* positions, int pos_stride, const int* seq_of_token, const int* q_start,
+                                    const int* slots, int n_tokens, int n_seqs, int* status, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (hdp > 32 * MAX_PER_LANE || dk > hdp || dv > hdp || dk <= 0 || dv <= 0 || (taps > 0 && w == nullptr) ||
+        (taps > 1 && tails == nullptr))
+        return (int)cudaErrorInvalidValue;
+    ConvKvParams p{proj, dt, proj_stride, w, w_dt, tails, tail_stride, C, taps, n_q, n_kv, dk, dv, hdp, unit_norm, eps,
+                   q_out, q_stride, cache, page_stride, (long)n_kv * page_size * hdp, num_pages, page_size, write_kv,
+                   block_table, table_stride, positions, pos_stride, seq_of_token, q_start, slots, n_tokens, status};
+    cudaStream_t s = (cudaStream_t)stream;
+    const long warps = (long)n_tokens * (n_q + (write_kv ? 2 * n_kv : 0));
+    conv_norm_kv_write_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(p);
+    int e = rs_launch_result();
+    if (e != 0 || taps <= 1) return e;
+    const long n = (long)n_seqs * C;
+    conv_tail_update_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(proj, dt, proj_stride, tails, tail_stride, q_start,
+                                                                         slots, C, taps, n_seqs);
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_sigmoid_gate(const void* a, long a_stride, const void* g, long g_stride, void* out, long out_stride, int dt,
+                              int n_heads, int dv, int hdp, int n_tokens, void* stream) {
+    if (n_tokens <= 0) return 0;
+    const long n = (long)n_tokens * n_heads * dv;
+    sigmoid_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, a_stride, g, g_stride, out,
+                                                                                        out_stride, dt, n_heads, dv, hdp,
+                                                                                        n_tokens);
+    return rs_launch_result();
+}

@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const int* __restrict__
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (int pr = threadIdx.x; pr < P; pr += blockDim.x) {
-        int id = ids[pr / top];
+        int id = ids != nullptr ? ids[pr / top] : pr / top;        // without ids the table has one row per token of the step
         if (id < 0 || id >= V) { atomicOr(status, RS_STATUS_BAD_TOKEN); id = 0; }
         int e = table[(size_t)id * top + pr % top];
         if (e < 0 || e >= E) { atomicOr(status, RS_STATUS_BAD_PLAN); e = 0; }
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const int* __restrict__
     __syncthreads();
     // Where a pair lands within its expert's rows changes no value: every pair's row is computed by itself.
     for (int pr = threadIdx.x; pr < P; pr += blockDim.x) {
-        int id = ids[pr / top];
+        int id = ids != nullptr ? ids[pr / top] : pr / top;
         if (id < 0 || id >= V) id = 0;
         int e = table[(size_t)id * top + pr % top];
         if (e < 0 || e >= E) e = 0;
@@ -83,7 +83,10 @@ struct GroupedParams {
     void* out; int out_dt; long out_stride;                  // [P, N]
     const int* order; const int* tiles; const int* n_tiles;
     int N, K, gated;          // gated: 0 plain; 1 gate rows [0, N) and up rows [N, 2N); 2 gate row 2n, up row 2n + 1
+    int relu2;                // plain products only: out = max(a W.T, 0)^2
 };
+
+__device__ __forceinline__ float relu_squared(float v) { v = fmaxf(v, 0.f); return v * v; }
 
 __device__ __forceinline__ size_t gate_row(const GroupedParams& p, int n) { return p.gated == 2 ? 2 * (size_t)n : (size_t)n; }
 __device__ __forceinline__ size_t up_row(const GroupedParams& p, int n) { return p.gated == 2 ? 2 * (size_t)n + 1 : (size_t)p.N + n; }
@@ -146,7 +149,7 @@ __global__ void __launch_bounds__(256) grouped_linear_tile_kernel(const GroupedP
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
             if (gn >= p.N) continue;
-            const float v = p.gated ? silu_exact(acc[i][j]) * accu[i][j] : acc[i][j];
+            const float v = p.gated ? silu_exact(acc[i][j]) * accu[i][j] : (p.relu2 ? relu_squared(acc[i][j]) : acc[i][j]);
             store_any(p.out, p.out_dt, (size_t)pr * p.out_stride + gn, v);
         }
     }
@@ -229,7 +232,7 @@ __global__ void __launch_bounds__(256) grouped_linear_rows_kernel(const GroupedP
             const float u = p.gated ? warp_sum(accu[c][r]) : 0.f;
             const int pr = pair_of_row[r];
             if (lane == 0 && gn < p.N && pr >= 0)
-                store_any(p.out, p.out_dt, (size_t)pr * p.out_stride + gn, p.gated ? silu_exact(g) * u : g);
+                store_any(p.out, p.out_dt, (size_t)pr * p.out_stride + gn, p.gated ? silu_exact(g) * u : (p.relu2 ? relu_squared(g) : g));
         }
     }
 }
@@ -240,19 +243,21 @@ RS_EXPORT int rs_grouped_linear_rows_per_tile(int small) { return small ? GR_ROW
 RS_EXPORT int rs_grouped_linear(const void* a, int a_dt, long a_stride, int a_div, const void* w, int w_dt,
                                 long w_expert_stride, void* out, int out_dt, long out_stride, const int* order,
                                 const int* tiles, const int* n_tiles, int max_tiles, int N, int K, int gated, int small,
-                                void* stream) {
+                                int relu2, void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
+    if (gated && relu2) return (int)cudaErrorInvalidValue;
     GroupedParams p{a, a_dt, a_stride, a_div, w, w_dt, w_expert_stride, out, out_dt, out_stride, order, tiles, n_tiles,
-                    N, K, gated};
+                    N, K, gated, relu2};
     cudaStream_t s = (cudaStream_t)stream;
     if (small) grouped_linear_rows_kernel<<<dim3((N + GR_COLS - 1) / GR_COLS, max_tiles), 256, 0, s>>>(p);
     else grouped_linear_tile_kernel<<<dim3((N + GL_BN - 1) / GL_BN, max_tiles), 256, 0, s>>>(p);
     return rs_launch_result();
 }
 
-// out[t, :] = weight * sum_k pair_out[t * top + k, :] + sigmoid(h[t, :] . gate_w) * shared[t, :]
+// out[t, :] = weight * sum_k (pair_w[t * top + k] or 1) * pair_out[t * top + k, :] + sigmoid(h[t, :] . gate_w) * shared[t, :]
 // (shared == null: no shared expert).  out is float32 [T, n].
 __global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair_stride, int top, float weight,
+                                   const float* __restrict__ pair_w,
                                    const void* __restrict__ shared, int shared_dt, long shared_stride,
                                    const void* __restrict__ h, int h_dt, long h_stride, const void* __restrict__ gate_w,
                                    int gate_dt, float* __restrict__ out, long out_stride, int n) {
@@ -270,18 +275,22 @@ __global__ void moe_combine_kernel(const float* __restrict__ pair_out, long pair
     }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < top; ++k) v += pair_out[(size_t)(t * top + k) * pair_stride + i];
+        if (pair_w != nullptr) {             // every pair with a weight of its own, k ascending
+            for (int k = 0; k < top; ++k) v = fmaf(pair_w[(size_t)t * top + k], pair_out[(size_t)(t * top + k) * pair_stride + i], v);
+        } else {
+            for (int k = 0; k < top; ++k) v += pair_out[(size_t)(t * top + k) * pair_stride + i];
+        }
         v *= weight;
         if (shared != nullptr) v = fmaf(gate, load_any(shared, shared_dt, (size_t)t * shared_stride + i), v);
         out[(size_t)t * out_stride + i] = v;
     }
 }
 
-RS_EXPORT int rs_moe_combine(const float* pair_out, long pair_stride, int top, float weight, const void* shared,
+RS_EXPORT int rs_moe_combine(const float* pair_out, long pair_stride, int top, float weight, const float* pair_w, const void* shared,
                              int shared_dt, long shared_stride, const void* h, int h_dt, long h_stride, const void* gate_w,
                              int gate_dt, float* out, long out_stride, int n_tokens, int n, void* stream) {
     if (n_tokens <= 0) return 0;
-    moe_combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(pair_out, pair_stride, top, weight, shared, shared_dt,
+    moe_combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(pair_out, pair_stride, top, weight, pair_w, shared, shared_dt,
                                                                   shared_stride, h, h_dt, h_stride, gate_w, gate_dt, out,
                                                                   out_stride, n);
     return rs_launch_result();

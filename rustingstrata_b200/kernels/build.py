@@ -33,6 +33,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "core": {"sources": ["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "sampling.cu", "sequence_parts.cu",
                          "moe_simt.cu"], "link": []},
+    # several residual streams, summed embedding tables, routers, convolved and gated attention (both engines)
+    "stream": {"sources": ["stream_parts.cu", "conv_attention_parts.cu"], "link": []},
     # tensor-core paths of the bfloat16 engine; the 32-bit engine never loads this library
     # not loaded by the engine: one kernel whose wait is never satisfied, built with a 2 ms limit, so that a test can
     # see the bounded-wait path end in a status bit and leave the context usable

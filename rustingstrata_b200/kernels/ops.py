@@ -99,8 +99,8 @@ def core():
                                        c_int, c_int, c_int, c_int, c_void_p]
         lib.rs_attention_simt.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                          c_void_p, c_void_p]
+                                          c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                          c_int, c_int, c_void_p, c_void_p]
         lib.rs_attention_simt_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_attention_simt_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_simt_partial_floats.restype = c_long
@@ -130,8 +130,8 @@ def core():
                                      c_int, c_void_p, c_void_p]
         lib.rs_grouped_linear_rows_per_tile.argtypes = [c_int]
         lib.rs_grouped_linear.argtypes = [c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
-                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
-        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_int, c_float, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rs_moe_combine.argtypes = [c_void_p, c_long, c_int, c_float, c_void_p, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
                                        c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_void_p]
         _core = lib
     return _core
@@ -725,7 +725,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
                    head_dim: int, page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor,
                    split_keys: int = 128, max_splits: int = 1, split_start: Optional[torch.Tensor] = None,
                    total_splits: int = 0, partial: Optional[torch.Tensor] = None,
-                   slopes: Optional[torch.Tensor] = None, one_plane: bool = False) -> None:
+                   slopes: Optional[torch.Tensor] = None, one_plane: bool = False,
+                   dist_bias: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention (see csrc/attention_simt.cu).  q/out: [T, >= n_q*head_dim] views.
 
     ``one_plane``: the cache is [pages, 1, n_kv, page_size, head_dim] and a row is key and value at once (a latent
@@ -733,6 +734,9 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
 
     ``slopes``: float32 [n_q] or None: slopes[h] * (key position - query position) is added to every scaled score of
     head h (a position encoding that biases scores by distance instead of rotating q and k).
+
+    ``dist_bias``: float32 [n_dist, n_q] or None: row min(query position - key position, n_dist - 1) is added to the
+    scaled scores, one value per head (a bias tabulated by distance; the last row serves every longer distance).
 
     Decode form: ``partial`` is the workspace of un-normalised partial results, one slot of n_q * (head_dim + 2)
     float32 values per (sequence, split); ``split_start[w]`` is the first slot of sequence w and ``total_splits`` the
@@ -756,6 +760,9 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
             raise KernelError(f"attention: {name} must be int32")
     if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != n_q or not slopes.is_contiguous() or not slopes.is_cuda):
         raise KernelError(f"attention: slopes must be contiguous float32 [{n_q}] on the device")
+    if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != n_q
+                                  or dist_bias.shape[0] < 1 or not dist_bias.is_contiguous() or not dist_bias.is_cuda):
+        raise KernelError(f"attention: dist_bias must be contiguous float32 [distances, {n_q}] on the device")
     slots = 0
     if decode:
         if split_start is None or split_start.dtype != torch.int32:
@@ -765,8 +772,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q), _ptr(cache), cache.stride(0), cache.shape[0],
         page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q,
         n_kv, head_dim, int(window), float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start),
-        _ptr(partial), slots, _ptr(slopes), 1 if one_plane else 0,
-        _ptr(status), _stream()), "attention_simt", 2 if decode else 1)
+        _ptr(partial), slots, _ptr(slopes), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0],
+        1 if one_plane else 0, _ptr(status), _stream()), "attention_simt", 2 if decode else 1)
 
 
 def _partial_slots(partial: Optional[torch.Tensor], total_splits: int, n_q: int, head_dim: int, who: str) -> int:
@@ -813,17 +820,18 @@ def attention_prefill_q_per_cta(dtype: torch.dtype, n_q: int, n_kv: int, head_di
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                       head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor,
-                      force: str = "", slopes: Optional[torch.Tensor] = None, one_plane: bool = False) -> None:
+                      force: str = "", slopes: Optional[torch.Tensor] = None, one_plane: bool = False,
+                      dist_bias: Optional[torch.Tensor] = None) -> None:
     """Attention of prompt portions; ``work`` lists (sequence, first query) tiles of ``attention_prefill_q_per_cta``
     tokens.  tcgen05 kernel (csrc/attention_prefill_tc.cu), mma.sync kernel (csrc/attention_prefill_mma.cu) or
     CUDA cores, whichever takes the shape; ``force`` names one.  Score biases (``slopes``) are the CUDA-core kernel's."""
     kind = attention_prefill_kernel(q.dtype, n_q, n_kv, head_dim, page_size, force)
-    if (slopes is not None or one_plane) and kind != "simt":
+    if (slopes is not None or one_plane or dist_bias is not None) and kind != "simt":
         raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score biases or reads a "
                           "one-plane cache")
     if kind == "simt":
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
-                       scale, False, status, slopes=slopes, one_plane=one_plane)
+                       scale, False, status, slopes=slopes, one_plane=one_plane, dist_bias=dist_bias)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status)
     _rows_contiguous(q, "q")
@@ -866,16 +874,17 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor, split_keys: int,
                      max_splits: int, split_start: torch.Tensor, total_splits: int, partial: torch.Tensor,
                      force_simt: bool = False, slopes: Optional[torch.Tensor] = None,
-                     items: Optional[torch.Tensor] = None, one_plane: bool = False) -> None:
+                     items: Optional[torch.Tensor] = None, one_plane: bool = False,
+                     dist_bias: Optional[torch.Tensor] = None) -> None:
     """Attention of sequences with one query token each: the tensor-core kernel (csrc/attention_decode_mma.cu)
     where it takes the shape, else the CUDA-core kernel's split form (always, when score biases are given).  Same
     partial-workspace layout.  ``items``: the step's list of live (sequence, kv head, split) items from
     :func:`attention_decode_items`, which a caller with several layers builds once per step; built here if not given."""
-    if (force_simt or slopes is not None or one_plane
+    if (force_simt or slopes is not None or one_plane or dist_bias is not None
             or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size)):
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
-                       total_splits=total_splits, partial=partial, slopes=slopes, one_plane=one_plane)
+                       total_splits=total_splits, partial=partial, slopes=slopes, one_plane=one_plane, dist_bias=dist_bias)
         return
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
     _rows_contiguous(q, "q")
@@ -1199,16 +1208,17 @@ def grouped_rows_per_tile(small: bool) -> int:
     return GROUPED_ROWS_SMALL if small else GROUPED_ROWS_TILED
 
 
-def moe_route(ids: torch.Tensor, table: torch.Tensor, n_experts: int, n_tokens: int, rows_per_tile: int,
+def moe_route(ids: Optional[torch.Tensor], table: torch.Tensor, n_experts: int, n_tokens: int, rows_per_tile: int,
               order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor, status: torch.Tensor) -> None:
     """Sorts the step's (token, k) pairs by the expert that ``table[ids[t], k]`` names: ``order`` [T * top] pair ids
-    grouped by expert, ``tiles`` [max_tiles, 3] (expert, first row in order, rows), ``n_tiles`` [1]."""
+    grouped by expert, ``tiles`` [max_tiles, 3] (expert, first row in order, rows), ``n_tiles`` [1].  Without ``ids``
+    the table has one row per token of the step (the choice a router made): pair (t, k) goes to ``table[t, k]``."""
     _cuda(ids, table, order, tiles, n_tiles, status)
     V, top = table.shape
     for name, t in (("ids", ids), ("table", table), ("order", order), ("tiles", tiles), ("n_tiles", n_tiles)):
-        if t.dtype != torch.int32 or not t.is_contiguous():
+        if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
             raise KernelError(f"moe_route: {name} must be contiguous int32")
-    if order.numel() < n_tokens * top or ids.numel() < n_tokens:
+    if order.numel() < n_tokens * top or (ids.numel() if ids is not None else V) < n_tokens:
         raise KernelError("moe_route: order must hold tokens * top entries")
     if rows_per_tile not in (grouped_rows_per_tile(True), grouped_rows_per_tile(False), GROUPED_ROWS_LARGE):
         raise KernelError("moe_route: rows_per_tile must be a tile size of the grouped product")
@@ -1218,11 +1228,14 @@ def moe_route(ids: torch.Tensor, table: torch.Tensor, n_experts: int, n_tokens: 
 
 def grouped_linear(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch.Tensor, order: torch.Tensor,
                    tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, small: bool,
-                   interleaved: bool = False) -> None:
+                   interleaved: bool = False, relu2: bool = False) -> None:
     """One product per expert over the rows ``moe_route`` dealt to it.  Pair p reads row p // a_div of ``a`` and writes
     row p of ``out``.  weight [E, N, K], or [E, 2N, K] when ``gated``: out = SiLU(a Wg.T) * (a Wu.T) with the gate rows
-    first and the up rows behind them, or alternating (gate 2n, up 2n + 1) when ``interleaved``."""
+    first and the up rows behind them, or alternating (gate 2n, up 2n + 1) when ``interleaved``.  ``relu2`` (plain
+    products only): out = max(a W.T, 0)^2."""
     _cuda(a, weight, out, order, tiles, n_tiles)
+    if gated and relu2:
+        raise KernelError("grouped_linear: the squared ReLU follows a plain product, not a gated one")
     _rows_contiguous(a, "grouped_linear a")
     _rows_contiguous(out, "grouped_linear out")
     if weight.dim() != 3 or not weight.is_contiguous():
@@ -1235,7 +1248,7 @@ def grouped_linear(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch
     _check(core().rs_grouped_linear(_ptr(a), dtype_code(a), a.stride(0), a_div, _ptr(weight), dtype_code(weight),
                                     weight.stride(0), _ptr(out), dtype_code(out), out.stride(0), _ptr(order), _ptr(tiles),
                                     _ptr(n_tiles), max_tiles, N, K, (2 if interleaved else 1) if gated else 0,
-                                    1 if small else 0, _stream()), "grouped_linear")
+                                    1 if small else 0, 1 if relu2 else 0, _stream()), "grouped_linear")
 
 
 def grouped_gemm_mma_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -1272,10 +1285,14 @@ def grouped_gemm_mma(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: tor
 
 def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tensor, n_tokens: int,
                 shared: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None,
-                gate_weight: Optional[torch.Tensor] = None) -> None:
+                gate_weight: Optional[torch.Tensor] = None, pair_weights: Optional[torch.Tensor] = None) -> None:
     """out[t] = weight * sum_k pair_out[t * top + k] + sigmoid(h[t] . gate_weight) * shared[t]  (float32 out; the
-    second term only with ``shared``, its factor 1 without ``gate_weight``)."""
-    _cuda(pair_out, out, shared, h, gate_weight)
+    second term only with ``shared``, its factor 1 without ``gate_weight``).  ``pair_weights`` float32 [T * top]:
+    every pair is multiplied by its own weight in the sum."""
+    _cuda(pair_out, out, shared, h, gate_weight, pair_weights)
+    if pair_weights is not None and (pair_weights.dtype != torch.float32 or not pair_weights.is_contiguous()
+                                     or pair_weights.numel() < n_tokens * top):
+        raise KernelError("moe_combine: pair_weights must be contiguous float32 [T * top]")
     _rows_contiguous(pair_out, "moe_combine pair_out")
     _rows_contiguous(out, "moe_combine out")
     n = out.shape[1]
@@ -1290,7 +1307,195 @@ def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tens
             _rows_contiguous(h, "moe_combine h")
             if gate_weight.numel() != n or not gate_weight.is_contiguous() or h.shape[1] != n:
                 raise KernelError("moe_combine: the gate reads h [T, n] with a weight of n values")
-    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), top, float(weight), _ptr(shared), _any_code(shared),
+    _check(core().rs_moe_combine(_ptr(pair_out), pair_out.stride(0), top, float(weight), _ptr(pair_weights), _ptr(shared),
+                                 _any_code(shared),
                                  0 if shared is None else shared.stride(0), _ptr(h if gate_weight is not None else None),
                                  _any_code(h), 0 if h is None else h.stride(0), _ptr(gate_weight), _any_code(gate_weight),
                                  _ptr(out), out.stride(0), n_tokens, n, _stream()), "moe_combine")
+
+
+# ----------------------------------------------------------------------------- several residual streams, summed embeddings
+_streamlib = None
+
+
+def streamlib():
+    global _streamlib
+    if _streamlib is None:
+        lib = load_library("stream")
+        lib.rs_embed_sum.argtypes = [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_long, c_long, c_void_p, c_int, c_int,
+                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long,
+                                     c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_stream_layernorm.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                            c_float, c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p]
+        lib.rs_stream_update.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                         c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_int, c_int, c_int,
+                                         c_void_p]
+        lib.rs_router_topk.argtypes = [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_void_p]
+        lib.rs_conv_norm_kv_write.argtypes = [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
+                                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p, c_long,
+                                              c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_void_p, c_void_p]
+        lib.rs_sigmoid_gate.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
+                                        c_void_p]
+        _streamlib = lib
+    return _streamlib
+
+
+MAX_STREAMS = 8            # residual streams the stream kernels take
+MAX_STREAM_WIDTH = 12288   # widest row they hold in shared memory
+
+
+def _i32(name: str, *ts) -> None:
+    for t in ts:
+        if t is not None and (t.dtype != torch.int32 or not t.is_cuda):
+            raise KernelError(f"{name}: index tensors must be int32 on the device")
+
+
+def embed_sum(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, n_tokens: int, n_seqs: int, copies: int,
+              positions: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+              status: torch.Tensor, bigram: Optional[torch.Tensor] = None, mul_prev: int = 0, mul_cur: int = 0,
+              prev_state: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None) -> None:
+    """out[t, c * D : (c + 1) * D] = table[ids[t]] + bigram[row(t)] + position_table[place(t)] for every copy c < copies
+    (float32).  ``bigram`` [buckets + 1, D]: row (previous token * mul_prev + token * mul_cur) mod buckets, the last
+    row for a sequence's first token; the previous token of a portion's first token is read from ``prev_state``
+    (int32 [slots, >= 1]), which then takes each sequence's last token.  ``positions`` [T, streams]: column 0 is the
+    token's place in its sequence.  Either table may be left out."""
+    _cuda(table, ids, out, positions, seq_of_token, q_start, slots, status, bigram, prev_state, position_table)
+    _i32("embed_sum", ids, positions, seq_of_token, q_start, slots, prev_state)
+    _rows_contiguous(out, "embed_sum out")
+    V, D = table.shape
+    if out.dtype != torch.float32 or out.shape[1] < copies * D or out.shape[0] < n_tokens or not table.is_contiguous():
+        raise KernelError(f"embed_sum: out {tuple(out.shape)} must be float32 with {copies} x {D} columns")
+    for name, t in (("bigram", bigram), ("position_table", position_table)):
+        if t is not None and (t.dim() != 2 or t.shape[1] != D or not t.is_contiguous()):
+            raise KernelError(f"embed_sum: {name} must be contiguous [rows, {D}]")
+    if bigram is not None and (prev_state is None or prev_state.dim() != 2 or bigram.shape[0] < 2):
+        raise KernelError("embed_sum: a bigram table needs the previous-token state [slots, >= 1] and at least two rows")
+    _check(streamlib().rs_embed_sum(
+        _ptr(table), dtype_code(table), V, _ptr(bigram), _any_code(bigram), 0 if bigram is None else bigram.shape[0] - 1,
+        int(mul_prev), int(mul_cur), _ptr(position_table), _any_code(position_table),
+        0 if position_table is None else position_table.shape[0], _ptr(ids), _ptr(positions), positions.stride(0),
+        _ptr(seq_of_token), _ptr(q_start), _ptr(slots), _ptr(prev_state), 0 if prev_state is None else prev_state.stride(0),
+        _ptr(out), out.stride(0), copies, D, n_tokens, n_seqs, _ptr(status), _stream()), "embed_sum",
+        2 if bigram is not None else 1)
+
+
+def _check_streams(who: str, x: torch.Tensor, S: int, D: int):
+    _rows_contiguous(x, f"{who} x")
+    if x.dtype != torch.float32 or x.shape[1] < S * D:
+        raise KernelError(f"{who}: x must be float32 with {S} x {D} columns")
+    if not 1 <= S <= MAX_STREAMS or not 1 <= D <= MAX_STREAM_WIDTH:
+        raise KernelError(f"{who}: {S} streams of width {D} (up to {MAX_STREAMS} streams, width up to {MAX_STREAM_WIDTH})")
+
+
+def stream_layernorm(x: torch.Tensor, n_streams: int, coef: Optional[torch.Tensor], weight: torch.Tensor,
+                     bias: Optional[torch.Tensor], eps: float, out: torch.Tensor, n_rows: int,
+                     rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = layer_norm(sum_s coef[s] * x[src(r), s * D : (s + 1) * D]) * weight + bias, src(r) = rows[r] or r.
+    x float32 [T, S * D]; coef [S] (None: every stream counts once); mean and variance (of the deviations) float32."""
+    _cuda(x, coef, weight, bias, out, rows)
+    D = weight.numel()
+    _check_streams("stream_layernorm", x, n_streams, D)
+    _rows_contiguous(out, "stream_layernorm out")
+    if out.shape[1] < D or out.shape[0] < n_rows or (coef is not None and coef.numel() != n_streams):
+        raise KernelError("stream_layernorm: out must hold n_rows x D values and coef one value per stream")
+    _i32("stream_layernorm", rows)
+    _check(streamlib().rs_stream_layernorm(_ptr(x), x.stride(0), _ptr(rows), _ptr(coef), _any_code(coef), _ptr(weight),
+                                           dtype_code(weight), _ptr(bias), _any_code(bias), float(eps), _ptr(out),
+                                           dtype_code(out), out.stride(0), n_streams, D, n_rows, _stream()),
+           "stream_layernorm")
+
+
+def stream_update(x: torch.Tensor, n_streams: int, y: torch.Tensor, mix: torch.Tensor, out_coef: torch.Tensor, n_rows: int,
+                  next_coef: Optional[torch.Tensor] = None, next_weight: Optional[torch.Tensor] = None,
+                  next_bias: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                  next_out: Optional[torch.Tensor] = None) -> None:
+    """All streams of a token at once from the old ones: x_t <- sum_s mix[s, t] * x_s + out_coef[t] * y  (x float32
+    [T, S * D] in place, y float32 [T, D], mix [S, S] indexed [from, to]).  With ``next_out`` also
+    next_out = layer_norm(sum_t next_coef[t] * x_t) * next_weight + next_bias of the new streams, in the same pass."""
+    _cuda(x, y, mix, out_coef, next_coef, next_weight, next_bias, next_out)
+    D = y.shape[1]
+    _check_streams("stream_update", x, n_streams, D)
+    _rows_contiguous(y, "stream_update y")
+    if y.dtype != torch.float32 or mix.numel() != n_streams * n_streams or out_coef.numel() != n_streams \
+            or not mix.is_contiguous() or min(x.shape[0], y.shape[0]) < n_rows:
+        raise KernelError("stream_update: y float32 [T, D], mix [S, S] contiguous, out_coef [S]")
+    if next_out is not None:
+        _rows_contiguous(next_out, "stream_update next_out")
+        if next_weight is None or next_weight.numel() != D or next_out.shape[1] < D or next_out.shape[0] < n_rows:
+            raise KernelError("stream_update: the next norm needs a weight of D values and an out of n_rows x D")
+    _check(streamlib().rs_stream_update(
+        _ptr(x), x.stride(0), _ptr(y), y.stride(0), _ptr(mix), dtype_code(mix), _ptr(out_coef), dtype_code(out_coef),
+        _ptr(next_coef), _any_code(next_coef), _ptr(next_weight), _any_code(next_weight), _ptr(next_bias),
+        _any_code(next_bias), float(next_eps), _ptr(next_out), _any_code(next_out),
+        0 if next_out is None else next_out.stride(0), n_streams, D, n_rows, _stream()), "stream_update")
+
+
+def router_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_tokens: int, choice: torch.Tensor,
+                weights: torch.Tensor, status: torch.Tensor) -> None:
+    """scores = softmax(logits[t]) (float32 [T, E]); choice[t] = the ``top`` experts with the largest score + correction
+    (int32 [T, top], the lower index on a tie); weights[t] = their scores / (sum of their scores + 1e-20)."""
+    _cuda(logits, correction, choice, weights, status)
+    _rows_contiguous(logits, "router_topk logits")
+    E = logits.shape[1]
+    if logits.dtype != torch.float32 or choice.dtype != torch.int32 or weights.dtype != torch.float32 \
+            or not choice.is_contiguous() or not weights.is_contiguous() or min(choice.numel(), weights.numel()) < n_tokens * top:
+        raise KernelError("router_topk: logits float32 [T, E], choice int32 and weights float32 [T * top] contiguous")
+    if not 1 <= top <= E <= 1024 or (correction is not None and correction.numel() != E):
+        raise KernelError(f"router_topk: top {top} of {E} experts (up to 1024), one correction per expert")
+    _check(streamlib().rs_router_topk(_ptr(logits), logits.stride(0), _ptr(correction), _any_code(correction), E, top,
+                                      n_tokens, _ptr(choice), _ptr(weights), _ptr(status), _stream()), "router_topk")
+
+
+def conv_norm_kv_write(proj: torch.Tensor, conv_weight: Optional[torch.Tensor], tails: Optional[torch.Tensor], n_q: int,
+                       n_kv: int, dk: int, dv: int, head_pad: int, unit_norm: bool, eps: float, q_out: torch.Tensor,
+                       cache: Optional[torch.Tensor], block_table: torch.Tensor, page_size: int, positions: torch.Tensor,
+                       seq_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, n_tokens: int, n_seqs: int,
+                       write_kv: bool, status: torch.Tensor) -> None:
+    """The projected rows ``proj`` [T, q heads * dk | kv heads * dk | kv heads * dv] (the key and value parts only with
+    ``write_kv``) pass a causal convolution over time per channel (``conv_weight`` [taps, C] tap-major, None: none;
+    ``tails`` float32 [slots, >= (taps - 1) * C] holds each request's last taps - 1 projected rows and is updated);
+    with ``unit_norm`` every q and k head is divided by sqrt(mean square + eps); q goes to ``q_out`` [T, n_q * head_pad],
+    k and v into the cache [pages, 2, n_kv, page_size, head_pad] at the tokens' places; padding is zero."""
+    _cuda(proj, conv_weight, tails, q_out, cache, block_table, positions, seq_of_token, q_start, slots, status)
+    _rows_contiguous(proj, "conv_norm_kv_write proj")
+    _rows_contiguous(q_out, "conv_norm_kv_write q_out")
+    _i32("conv_norm_kv_write", block_table, positions, seq_of_token, q_start, slots)
+    C = n_q * dk + (n_kv * (dk + dv) if write_kv else 0)
+    taps = 0 if conv_weight is None else conv_weight.shape[0]
+    if proj.shape[1] < C or q_out.shape[1] < n_q * head_pad or q_out.dtype != proj.dtype or min(proj.shape[0], q_out.shape[0]) < n_tokens:
+        raise KernelError(f"conv_norm_kv_write: proj {tuple(proj.shape)} / q_out {tuple(q_out.shape)} do not fit {C} channels")
+    if head_pad % 16 or head_pad > 256 or max(dk, dv) > head_pad:
+        raise KernelError(f"conv_norm_kv_write: head sizes {dk}/{dv} in rows of {head_pad} (a multiple of 16 up to 256)")
+    if conv_weight is not None and (tuple(conv_weight.shape) != (taps, C) or not conv_weight.is_contiguous()):
+        raise KernelError(f"conv_norm_kv_write: the convolution's weight must be contiguous [taps, {C}]")
+    if taps > 1 and (tails is None or tails.dtype != torch.float32 or tails.dim() != 2 or tails.stride(1) != 1
+                     or tails.shape[1] < (taps - 1) * C):
+        raise KernelError("conv_norm_kv_write: tails must be float32 [slots, >= (taps - 1) * channels]")
+    if write_kv and (cache is None or cache.dtype != proj.dtype or not cache.is_contiguous()
+                     or tuple(cache.shape[1:]) != (2, n_kv, page_size, head_pad)):
+        raise KernelError(f"conv_norm_kv_write: the cache must be [pages, 2, {n_kv}, {page_size}, {head_pad}] of the rows' type")
+    _check(streamlib().rs_conv_norm_kv_write(
+        _ptr(proj), dtype_code(proj), proj.stride(0), _ptr(conv_weight), _any_code(conv_weight), _ptr(tails),
+        0 if tails is None else tails.stride(0), C, taps, n_q, n_kv, dk, dv, head_pad, 1 if unit_norm else 0, float(eps),
+        _ptr(q_out), q_out.stride(0), _ptr(cache), 0 if cache is None else cache.stride(0),
+        0 if cache is None else cache.shape[0], page_size, 1 if write_kv else 0, _ptr(block_table), block_table.stride(0),
+        _ptr(positions), positions.stride(0), _ptr(seq_of_token), _ptr(q_start), _ptr(slots), n_tokens, n_seqs, _ptr(status),
+        _stream()), "conv_norm_kv_write", 2 if taps > 1 else 1)
+
+
+def sigmoid_gate(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, n_heads: int, dv: int, head_pad: int,
+                 n_tokens: int) -> None:
+    """out[t, h * dv + d] = a[t, h * head_pad + d] * sigmoid(gate[t, h * dv + d]) (None: times 1), sigmoid in float32."""
+    _cuda(a, gate, out)
+    _rows_contiguous(a, "sigmoid_gate a")
+    _rows_contiguous(out, "sigmoid_gate out")
+    if gate is not None:
+        _rows_contiguous(gate, "sigmoid_gate gate")
+    if a.shape[1] < n_heads * head_pad or out.shape[1] < n_heads * dv or (gate is not None and (gate.shape[1] < n_heads * dv
+                                                                                               or gate.dtype != a.dtype)) \
+            or out.dtype != a.dtype:
+        raise KernelError("sigmoid_gate: a [T, heads * head_pad], gate and out [T, heads * dv], one element type")
+    _check(streamlib().rs_sigmoid_gate(_ptr(a), a.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(out),
+                                       out.stride(0), dtype_code(a), n_heads, dv, head_pad, n_tokens, _stream()), "sigmoid_gate")

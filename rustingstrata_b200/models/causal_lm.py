@@ -41,7 +41,12 @@ class CausalLM:
             self.blocks.append(block_cls(ls.block, runtime, built))
         self.final_norm = mk("norm", spec.final_norm)
         self.head = mk("head", spec.head)
-        runtime.scratch("residual", runtime.max_batch_tokens, spec.hidden_size, torch.float32)
+        self.n_streams = int(getattr(spec, "n_streams", 1))
+        if self.n_streams > 1 and int(getattr(self.embedding, "copies", 1)) != self.n_streams:
+            raise ValueError(f"the model keeps {self.n_streams} residual streams, but its embedding part fills "
+                             f"{getattr(self.embedding, 'copies', 1)}")
+        self.stream_width = spec.hidden_size * self.n_streams
+        runtime.scratch("residual", runtime.max_batch_tokens, self.stream_width, torch.float32)
         runtime.scratch("head_in", runtime.max_logit_rows, spec.hidden_size)
         runtime.scratch("logits", runtime.max_logit_rows, spec.vocab_size, torch.float32)
         # position values a step carries per token: the most any position encoding of the model asks for
@@ -100,6 +105,11 @@ class CausalLM:
             if lc.cache is not None and not any_cache:
                 raise ValueError(f"run order entry {i} names a cache but its mixer keeps none")
             self.calls.append(entry)
+        # state an embedding keeps per request (e.g. the previous token), under a key no run-order entry has
+        self.embedding_state_key = (-1, "embedding")
+        need = self.embedding.state_need() if hasattr(self.embedding, "state_need") else None
+        if need is not None:
+            self.state_needs[self.embedding_state_key] = need
 
     # ---------------------------------------------------------------- weights
     def parts(self):
@@ -152,6 +162,8 @@ class CausalLM:
                     g, j = self._cache_slot[key]
                     info.cache = caches[g][j]
                 info.state = states.get(key)
+        if self.embedding_state_key in states:
+            self.embedding.state = states[self.embedding_state_key]
 
     # ---------------------------------------------------------------- one step
     def plan(self, batch: HostBatch) -> Dict:
@@ -165,9 +177,12 @@ class CausalLM:
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """Runs the step's tokens and returns float32 logits [n_logit_rows, vocab] (None if none are wanted)."""
         rt = self.runtime
-        residual = rt.get_scratch("residual", torch.float32)[:, : self.spec.hidden_size]
+        residual = rt.get_scratch("residual", torch.float32)[:, : self.stream_width]
         self.embedding.forward(ctx, residual)
+        ctx.normed_ready = False
         for k, info in enumerate(self.calls):
+            nxt = self.blocks[self.calls[k + 1].layer] if k + 1 < len(self.calls) else None
+            ctx.next_reader = nxt.stream_reader() if nxt is not None and hasattr(nxt, "stream_reader") else None
             # a block's last product may leave its final sum to the next block's first norm, if that norm can take it
             ctx.next_block_takes_owed = (k + 1 < len(self.calls)
                                          and self.blocks[self.calls[k + 1].layer].first_reader_takes_owed)
@@ -176,7 +191,10 @@ class CausalLM:
                 if ctx.owed is not None:
                     ctx.owed.finish()
                     ctx.owed = None
-                ctx.on_layer(k, residual[: ctx.n_tokens])
+                x = residual[: ctx.n_tokens]
+                if self.n_streams > 1:        # the callback sees the sum of the streams
+                    x = x.view(ctx.n_tokens, self.n_streams, self.spec.hidden_size).sum(dim=1)
+                ctx.on_layer(k, x)
         if ctx.owed is not None:
             ctx.owed.finish()
             ctx.owed = None

@@ -134,9 +134,18 @@ class PagedAttention(Mixer):
         position - query position) added to every scaled score.  The CUDA-core attention kernels take it."""
         return getattr(self.position, "score_slopes", None) if self.position is not None else None
 
+    def _distance_bias(self):
+        """A bias on the scores tabulated by distance, if the mixer has one: float32 [distances, n_heads] on the device;
+        row min(query position - key position, last row) is added to every scaled score."""
+        return None
+
+    def _cuda_cores_only(self) -> bool:
+        """Whether only the CUDA-core attention kernels can run this mixer (a score bias they alone add, a one-plane cache)."""
+        return self._score_slopes() is not None or self.one_plane or self._distance_bias() is not None
+
     def plan_key(self):
         if self.q_per_cta is None:
-            force = "simt" if self._score_slopes() is not None or self.one_plane else ""
+            force = "simt" if self._cuda_cores_only() else ""
             self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd,
                                                               self.runtime.page_size, force)
         return ("paged_attention", self.q_per_cta, self.window)
@@ -208,9 +217,10 @@ class PagedAttention(Mixer):
                       n_q=self.n_heads, n_kv=self.n_kv, head_dim=self.hd, page_size=rt.page_size, window=self.window,
                       scale=self.scale, status=ctx.status, one_plane=self.one_plane)
         slopes = self._score_slopes()
-        simt = slopes is not None or self.one_plane
+        dist_bias = self._distance_bias()
+        simt = self._cuda_cores_only()
         if plan["n_prefill"]:
-            ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes,
+            ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes, dist_bias=dist_bias,
                                   force="simt" if simt else "", **common)
         if plan["n_decode"]:
             items = None
@@ -222,6 +232,6 @@ class PagedAttention(Mixer):
                     plan[("items", self.n_kv)] = True
             ops.attention_decode(work=plan["decode_work"], n_work=plan["n_decode"], split_keys=SPLIT_KEYS,
                                  max_splits=plan["max_splits"], split_start=plan["split_start"],
-                                 total_splits=plan["total_splits"], slopes=slopes, items=items,
+                                 total_splits=plan["total_splits"], slopes=slopes, dist_bias=dist_bias, items=items,
                                  partial=rt.get_scratch("attn_partial", torch.float32), **common)
         return out

@@ -139,6 +139,11 @@ class StepContext:
     # A block that norms a sublayer's output before it joins the stream hands the mixer or feed-forward a buffer of
     # its own in place of the stream and sets ``store_output``: the part then stores its output there instead of adding.
     store_output: bool = False
+    # A block that rewrites the whole stream at its end can run the first norm of the next block in the same pass:
+    # ``next_reader`` (set by the model before each block) is what that block's ``stream_reader()`` returned, or None;
+    # ``normed_ready`` is set by the block that did so and cleared by the block that finds its input normed already.
+    next_reader: Any = None
+    normed_ready: bool = False
     # Called as on_layer(index in the run order, residual stream) after every entry of the run order, when set
     # (tests and debugging read the stream layer by layer; a step that sets it is not captured).
     on_layer: Any = None

@@ -167,3 +167,117 @@ class TableMoE(FeedForward):
             ops.residual_add(residual, delta, T)
 
 
+
+
+@register_part("feed_forward", "routed_moe")
+class RoutedMoE(FeedForward):
+    """A mixture of experts chosen per token by a softmax router, with an optional shared expert.
+
+    Router logits z = W_r h and scores s = softmax(z) over all experts are float32 in both engines.  The ``top``
+    experts with the largest s + correction are chosen (``correction``: one learned number per expert that steers the
+    choice only); their weights are their scores s divided by the sum of the chosen scores (+ 1e-20).  An expert is
+    down(relu(up h)^2) without biases; a shared expert of the same form runs for every token and is added unweighted.
+
+    params: hidden, experts, top, expert_ff, shared_ff (0 or None: no shared expert), correction (bool).
+    tensors: router [experts, hidden], correction [experts]; expert_up / expert_down: name patterns with ``{e}`` for the
+    expert's number; shared_up, shared_down.  The step's (token, k) pairs are sorted by expert on the device and one
+    grouped product per projection serves all experts, as in :class:`TableMoE`."""
+    SMALL_PAIRS_PER_EXPERT = TableMoE.SMALL_PAIRS_PER_EXPERT
+    LARGE_PAIRS_PER_EXPERT = TableMoE.LARGE_PAIRS_PER_EXPERT
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.n_experts, self.top = int(p["experts"]), int(p["top"])
+        self.ff = int(p["expert_ff"])
+        self.shared_ff = int(p.get("shared_ff") or 0)
+        self.has_correction = bool(p.get("correction", False))
+        if not 1 <= self.top <= self.n_experts <= 1024:
+            raise ValueError(f"routed_moe: top {self.top} of {self.n_experts} experts (up to 1024)")
+        rt = runtime
+        pairs = rt.max_batch_tokens * self.top
+        self.act_name = f"moe_act_{self.ff}"
+        rt.scratch(self.act_name, pairs, self.ff)
+        rt.scratch("moe_pair_out", pairs, self.hidden, torch.float32)
+        rt.scratch("moe_order", 1, pairs, torch.int32)
+        rt.scratch("moe_tiles", 1, 3 * self._max_tiles(pairs, min(_ROWS_PER_TILE.values())) + 4, torch.int32)
+        rt.scratch("moe_delta", rt.max_batch_tokens, self.hidden, torch.float32)
+        rt.scratch("router_logits", rt.max_batch_tokens, self.n_experts, torch.float32)
+        rt.scratch("router_choice", 1, pairs, torch.int32)
+        rt.scratch("router_weights", 1, pairs, torch.float32)
+        if self.shared_ff:
+            rt.scratch("moe_shared_act", rt.max_batch_tokens, self.shared_ff)
+            rt.scratch("moe_shared_out", rt.max_batch_tokens, self.hidden, torch.float32)
+
+    def _max_tiles(self, pairs: int, rows: int) -> int:
+        return pairs // rows + min(self.n_experts, pairs)
+
+    def tensor_needs(self):
+        t = self.spec.tensors
+        needs = {t["router"]: TensorNeed((self.n_experts, self.hidden))}
+        if self.has_correction:
+            needs[t["correction"]] = TensorNeed((self.n_experts,))
+        for e in range(self.n_experts):
+            needs[t["expert_up"].format(e=e)] = TensorNeed((self.ff, self.hidden))
+            needs[t["expert_down"].format(e=e)] = TensorNeed((self.hidden, self.ff))
+        if self.shared_ff:
+            needs[t["shared_up"]] = TensorNeed((self.shared_ff, self.hidden))
+            needs[t["shared_down"]] = TensorNeed((self.hidden, self.shared_ff))
+        return needs
+
+    def load(self, tensors):
+        t, E = self.spec.tensors, self.n_experts
+        self.w_router = tensors[t["router"]].contiguous()
+        self.correction = tensors[t["correction"]].to(torch.float32).contiguous() if self.has_correction else None
+        self.w_up = torch.stack([tensors[t["expert_up"].format(e=e)] for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[t["expert_down"].format(e=e)] for e in range(E)]).contiguous()
+        # bfloat16 engine with 16-byte aligned rows: the grouped products run on the tensor cores
+        self.tensor_cores = (self.w_up.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16
+                             and self.hidden % 8 == 0 and self.ff % 8 == 0)
+        if self.shared_ff:
+            self.w_shared_up = tensors[t["shared_up"]].contiguous()
+            self.w_shared_down = tensors[t["shared_down"]].contiguous()
+
+    def flops_per_token(self) -> float:
+        return 2.0 * (2 * self.top * self.ff * self.hidden + 2 * self.shared_ff * self.hidden + self.n_experts * self.hidden)
+
+    def forward(self, h, residual, ctx: StepContext):
+        rt, T, top = self.runtime, ctx.n_tokens, self.top
+        pairs = T * top
+        tensor_cores = self.tensor_cores
+        small = not tensor_cores and pairs <= self.SMALL_PAIRS_PER_EXPERT * self.n_experts
+        large = tensor_cores and pairs >= self.LARGE_PAIRS_PER_EXPERT * self.n_experts
+        rows = ops.GROUPED_ROWS_LARGE if large else _ROWS_PER_TILE[small]
+        max_tiles = self._max_tiles(pairs, rows)
+        order = rt.get_scratch("moe_order", torch.int32).view(-1)
+        tiles = rt.get_scratch("moe_tiles", torch.int32).view(-1)
+        n_tiles, tiles = tiles[:1], tiles[4:]
+        act = rt.get_scratch(self.act_name)[:, : self.ff]
+        pair_out = rt.get_scratch("moe_pair_out", torch.float32)[:, : self.hidden]
+        logits = rt.get_scratch("router_logits", torch.float32)[:, : self.n_experts]
+        choice = rt.get_scratch("router_choice", torch.int32).view(-1)[:pairs]
+        weights = rt.get_scratch("router_weights", torch.float32).view(-1)[:pairs]
+        ops.linear(h, self.w_router, logits, T, status=ctx.status)
+        ops.router_topk(logits, self.correction, top, T, choice, weights, ctx.status)
+        ops.moe_route(None, choice.view(T, top), self.n_experts, T, rows, order, tiles, n_tiles, ctx.status)
+        if tensor_cores:
+            ops.grouped_gemm_mma(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, large=large)
+            ops.relu_squared(act, act, pairs)
+            ops.grouped_gemm_mma(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, large=large)
+        else:
+            ops.grouped_linear(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, small=small, relu2=True)
+            ops.grouped_linear(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, small=small)
+        shared_out = None
+        if self.shared_ff:
+            sact = rt.get_scratch("moe_shared_act")[:, : self.shared_ff]
+            shared_out = rt.get_scratch("moe_shared_out", torch.float32)[:, : self.hidden]
+            ops.linear(h, self.w_shared_up, sact, T, status=ctx.status)
+            ops.relu_squared(sact, sact, T)
+            ops.linear(sact, self.w_shared_down, shared_out, T, status=ctx.status)
+        if ctx.store_output:
+            ops.moe_combine(pair_out, top, 1.0, residual, T, shared=shared_out, pair_weights=weights)
+        else:
+            delta = rt.get_scratch("moe_delta", torch.float32)[:, : self.hidden]
+            ops.moe_combine(pair_out, top, 1.0, delta, T, shared=shared_out, pair_weights=weights)
+            ops.residual_add(residual, delta, T)

@@ -29,7 +29,8 @@ class TensorNeed:
     """A tensor a part wants from the checkpoint.
 
     role: "matrix" (projection, drawn N(0, std) in random mode), "embedding"
-    (token table, same distribution), "norm" (scale vector, ones or 1+N(0, s)),
+    (token table, same distribution), "norm" (scale vector, ones or 1+N(0, s)), "average" (weights of a mean over
+    the first axis: 1/rows + N(0, s)),
     "int_table" (integer table kept as int32), "choice_table" (integer table whose rows each hold
     distinct values below ``limit``, e.g. the experts of a token).
     ``optional``: the checkpoint may leave the tensor out; the part then finds it missing in ``load``.
@@ -88,6 +89,9 @@ class ModelSpec:
     order: Tuple[LayerCall, ...]
     final_norm: PartSpec
     head: PartSpec
+    # residual streams per token: the stream buffer is [tokens, n_streams * hidden_size]; with more than one, the
+    # embedding fills every stream, the blocks read and write all of them, and the final norm reads their sum
+    n_streams: int = 1
 
 
 @dataclass(frozen=True)

@@ -77,6 +77,8 @@ def scale_shift(need: TensorNeed, std: float, norm_std: float) -> Tuple[float, f
     """(scale, shift) of value = shift + scale * normal for a tensor of this role."""
     if need.role == "norm":
         return float(norm_std), 1.0
+    if need.role == "average":          # weights of a mean over the first axis, 1 / rows + N(0, norm_std)
+        return float(norm_std), 1.0 / max(1, int(need.shape[0]) if len(need.shape) else 1)
     return float(std), 0.0
 
 
