@@ -134,6 +134,8 @@ class HyperConnectionBlock(Block):
         t = spec.tensors
         self.named = {q: all(f"{q}_{k}" in t for k in ("in", "out", "mix")) for q in ("mixer", "ff")}
         for q, full in self.named.items():
+            if q == "ff" and not self.has_ff:
+                continue
             if not full and (any(f"{q}_{k}" in t for k in ("in", "out", "mix")) or self.S != 1):
                 raise ValueError(f"block 'hyper_connection': {self.S} streams need the {q} sublayer's in, out and mix tensors")
         self.coef = {}

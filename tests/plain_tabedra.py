@@ -92,6 +92,8 @@ def attention(h, k, v, weights, prefix, m, eps):
     q = unit_rms(q.reshape(T, H, dk), eps)
     window = int(m["mask"]["size"]) if m.get("mask") else None
     rel = weights.get(prefix + "rel")
+    if rel is not None:          # the bias of every distance that can occur, [T, H]
+        by_distance = rel[torch.tensor([distance_bucket(n, rel.shape[0], float(m["bias_max"])) for n in range(T)])]
     out = torch.zeros(T, H, dv, dtype=F64)
     for hd in range(H):
         g = hd // (H // G)
@@ -99,8 +101,7 @@ def attention(h, k, v, weights, prefix, m, eps):
             lo = 0 if window is None else max(0, i - window + 1)
             s = (k[lo:i + 1, g] @ q[i, hd]) * float(m["scale"])
             if rel is not None:
-                s = s + torch.stack([rel[distance_bucket(i - j, rel.shape[0], float(m["bias_max"])), hd]
-                                     for j in range(lo, i + 1)])
+                s = s + by_distance[torch.arange(i - lo, -1, -1), hd]        # key j lies i - j back
             p = torch.softmax(s, dim=0)
             out[i, hd] = p @ v[lo:i + 1, g]
     y = out.reshape(T, H * dv)
