@@ -51,6 +51,7 @@ struct DecodeParams {
     int n_q, n_kv, group;
     int window;
     float scale_log2;                  // scale * log2(e)
+    const float* dist_bias; int n_dist; // [n_dist][n_q] or null: row min(query - key position, n_dist - 1) is added to the scaled scores
     const int* split_start;
     const int* items;                  // [split_start[n_work] * n_kv] live items, packed by pack_item
     float* partial;                    // [slot][n_q][hd + 2]: acc, max (log2 units), sum
@@ -331,7 +332,15 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) decode_attention_kernel(const 
                         for (int i = 0; i < 4; ++i) {
                             const int kpos = it.k_base + j0 + 8 * nt + 2 * t + (i & 1);
                             const bool vis = kpos >= it.key_lo && kpos < it.key_hi;
-                            sc[nt][i] = vis ? sc[nt][i] * p.scale_log2 : -INFINITY;
+                            float v = sc[nt][i] * p.scale_log2;
+                            if (p.dist_bias != nullptr) {
+                                // row (lane / 4) + 8 (i / 2) of the query operand is that head of the kv group
+                                const int hrow = (lane >> 2) + 8 * (i >> 1);
+                                if (vis && hrow < p.group)
+                                    v = fmaf(__ldg(p.dist_bias + (size_t)min(it.kv_len - 1 - kpos, p.n_dist - 1) * p.n_q +
+                                                   it.kvh * p.group + hrow), 1.4426950408889634f, v);
+                            }
+                            sc[nt][i] = vis ? v : -INFINITY;
                             m_row[i >> 1] = fmaxf(m_row[i >> 1], sc[nt][i]);
                         }
 #pragma unroll
@@ -656,8 +665,9 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
                                        int table_stride, const int* q_start, const int* kv_len, const int* work,
                                        int n_work, int n_q, int n_kv, int hd, int window, float scale, int split_keys,
                                        int max_splits, const int* split_start, const int* items, float* partial,
-                                       int partial_slots, int* status, void* stream) {
+                                       int partial_slots, const float* dist_bias, int n_dist, int* status, void* stream) {
     if (n_work <= 0) return 0;
+    if (dist_bias != nullptr && n_dist <= 0) return (int)cudaErrorInvalidValue;
     if (!rs_attention_decode_bf16_supported(n_q, n_kv, hd, page_size) || split_keys != SPLIT || max_splits <= 0 ||
         partial == nullptr || partial_slots <= 0 || split_start == nullptr || items == nullptr || n_kv > ITEM_MAX_KV ||
         n_work > ITEM_MAX_SEQS || max_splits > ITEM_MAX_SPLITS || (q_stride % 8) || ((long)q & 15) || ((long)cache & 15) ||
@@ -669,6 +679,7 @@ RS_EXPORT int rs_attention_decode_bf16(const void* q, long q_stride, void* out, 
     p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.dist_bias = dist_bias; p.n_dist = n_dist;
     p.split_start = split_start; p.items = items; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
     p.n_work = n_work; p.max_splits = max_splits;
     p.total = n_work * n_kv * max_splits;          // an upper bound, for the size of the grid

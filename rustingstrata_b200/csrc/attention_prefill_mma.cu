@@ -29,6 +29,7 @@ struct PrefillParams {
     int n_q, n_kv, group, pack, tokens_per_cta;
     int window;
     float scale_log2;
+    const float* dist_bias; int n_dist;    // [n_dist][n_q] or null: row min(query - key position, n_dist - 1) is added to the scaled scores
     int* status;
 };
 
@@ -118,6 +119,9 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     const int wq_lo = qpos0 + (16 * warp) / p.pack;
     const int wq_hi = qpos0 + min(n_rows - 1, 16 * warp + 15) / p.pack;
     const bool warp_live = 16 * warp < n_rows;
+    // the distance bias of this lane's two rows: a column of the table per head
+    const float* bias_a = p.dist_bias != nullptr ? p.dist_bias + head0 + ra % p.pack : nullptr;
+    const float* bias_b = p.dist_bias != nullptr ? p.dist_bias + head0 + rb % p.pack : nullptr;
 
     for (int blk = blk_lo; blk < blk_hi; ++blk) {
         const int stage = (blk - blk_lo) & 1;
@@ -147,6 +151,18 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
             }
             const bool need_mask = (k0 + BKV - 1 > wq_lo) || (k0 + BKV > key_hi) || (p.window > 0 && k0 <= wq_hi - p.window) ||
                                    k0 < key_lo;
+            if (bias_a != nullptr) {
+#pragma unroll
+                for (int nt = 0; nt < BKV / 8; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int kpos = k0 + 8 * nt + 2 * t + (i & 1);
+                        const int dist = min(max(((i >> 1) ? qpos_b : qpos_a) - kpos, 0), p.n_dist - 1);
+                        const float b = __ldg(((i >> 1) ? bias_b : bias_a) + (size_t)dist * p.n_q);
+                        // scores are in units of log2 from here on: (s * scale + b) * log2(e)
+                        s[nt][i] = fmaf(b, 1.4426950408889634f / p.scale_log2, s[nt][i]);
+                    }
+            }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int nt = 0; nt < BKV / 8; ++nt)
@@ -246,9 +262,10 @@ RS_EXPORT int rs_attention_prefill_bf16_q_per_cta(int n_q, int n_kv) { return RO
 RS_EXPORT int rs_attention_prefill_bf16(const void* q, long q_stride, void* out, long out_stride, const void* cache,
                                         long page_stride, int num_pages, int page_size, const int* block_table,
                                         int table_stride, const int* q_start, const int* kv_len, const int* work,
-                                        int n_work, int n_q, int n_kv, int hd, int window, float scale, int* status,
-                                        void* stream) {
+                                        int n_work, int n_q, int n_kv, int hd, int window, float scale,
+                                        const float* dist_bias, int n_dist, int* status, void* stream) {
     if (n_work <= 0) return 0;
+    if (dist_bias != nullptr && (n_dist <= 0 || scale == 0.f)) return (int)cudaErrorInvalidValue;
     if (!rs_attention_prefill_bf16_supported(n_q, n_kv, hd) || (q_stride % 2) || (out_stride % 2) || ((long)q & 3) ||
         ((long)out & 3) || ((long)cache & 15) || (page_stride % 8))
         return (int)cudaErrorInvalidValue;
@@ -258,6 +275,7 @@ RS_EXPORT int rs_attention_prefill_bf16(const void* q, long q_stride, void* out,
     p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.kv_len = kv_len; p.work = work;
     p.n_q = n_q; p.n_kv = n_kv; p.group = n_q / n_kv; p.pack = pack_of(p.group); p.tokens_per_cta = ROWS / p.pack;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.dist_bias = dist_bias; p.n_dist = n_dist;
     cudaStream_t s = (cudaStream_t)stream;
     switch (hd) {
         case 32: return launch<32>(p, n_work, s);

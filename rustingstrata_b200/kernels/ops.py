@@ -332,12 +332,12 @@ def bf16lib():
         lib.rs_attention_decode_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                 c_void_p, c_void_p]
+                                                 c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_attention_decode_build_items.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_attention_decode_bf16_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                  c_int, c_int, c_float, c_void_p, c_void_p]
+                                                  c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_attention_prefill_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                 c_int, c_float, c_void_p, c_void_p]
@@ -790,7 +790,12 @@ def _partial_slots(partial: Optional[torch.Tensor], total_splits: int, n_q: int,
 
 def attention_prefill_kernel(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int, force: str = "") -> str:
     """Which kernel ``attention_prefill`` runs for this shape: "tc" (tcgen05, head 64/128, page size a power of
-    two from 8 to 128), "mma" (mma.sync, head 32/64/96/128) or "simt" (everything else, and float32)."""
+    two from 8 to 128), "mma" (mma.sync, head 32/64/96/128) or "simt" (everything else, and float32).  ``force``
+    names one; "biased" asks for the fastest kernel that adds a bias tabulated by distance ("mma", else "simt")."""
+    if force == "biased":
+        if dtype == torch.bfloat16 and bf16lib().rs_attention_prefill_bf16_supported(n_q, n_kv, head_dim):
+            return "mma"
+        return "simt"
     if force:
         return force
     if dtype == torch.bfloat16:
@@ -826,9 +831,12 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     tokens.  tcgen05 kernel (csrc/attention_prefill_tc.cu), mma.sync kernel (csrc/attention_prefill_mma.cu) or
     CUDA cores, whichever takes the shape; ``force`` names one.  Score biases (``slopes``) are the CUDA-core kernel's."""
     kind = attention_prefill_kernel(q.dtype, n_q, n_kv, head_dim, page_size, force)
-    if (slopes is not None or one_plane or dist_bias is not None) and kind != "simt":
-        raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score biases or reads a "
+    if (slopes is not None or one_plane) and kind != "simt":
+        raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score slopes or reads a "
                           "one-plane cache")
+    if dist_bias is not None and kind == "tc":
+        raise KernelError("attention_prefill: a bias tabulated by distance is added by the mma.sync and CUDA-core kernels "
+                          "(force='biased')")
     if kind == "simt":
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, False, status, slopes=slopes, one_plane=one_plane, dist_bias=dist_bias)
@@ -853,7 +861,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     _check(bf16lib().rs_attention_prefill_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,
-        int(window), float(scale), _ptr(status), _stream()), "attention_prefill_bf16")
+        int(window), float(scale), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(status), _stream()),
+        "attention_prefill_bf16")
 
 
 def attention_decode_fast_ok(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int = 16) -> bool:
@@ -880,7 +889,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
     where it takes the shape, else the CUDA-core kernel's split form (always, when score biases are given).  Same
     partial-workspace layout.  ``items``: the step's list of live (sequence, kv head, split) items from
     :func:`attention_decode_items`, which a caller with several layers builds once per step; built here if not given."""
-    if (force_simt or slopes is not None or one_plane or dist_bias is not None
+    if (force_simt or slopes is not None or one_plane
             or not attention_decode_fast_ok(q.dtype, n_q, n_kv, head_dim, page_size)):
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, True, status, split_keys=split_keys, max_splits=max_splits, split_start=split_start,
@@ -906,8 +915,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
     _check(bf16lib().rs_attention_decode_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv, head_dim,
-        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(items), _ptr(partial), slots, _ptr(status),
-        _stream()), "attention_decode_bf16", 2)
+        int(window), float(scale), split_keys, max_splits, _ptr(split_start), _ptr(items), _ptr(partial), slots,
+        _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(status), _stream()), "attention_decode_bf16", 2)
 
 
 def attention_latent_ok(dtype: torch.dtype, n_heads: int, lat: int, page_size: int) -> bool:

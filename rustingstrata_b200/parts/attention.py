@@ -140,12 +140,21 @@ class PagedAttention(Mixer):
         return None
 
     def _cuda_cores_only(self) -> bool:
-        """Whether only the CUDA-core attention kernels can run this mixer (a score bias they alone add, a one-plane cache)."""
-        return self._score_slopes() is not None or self.one_plane or self._distance_bias() is not None
+        """Whether only the CUDA-core attention kernels can run this mixer (score slopes they alone add, a one-plane cache)."""
+        return self._score_slopes() is not None or self.one_plane
+
+    def _prefill_kernel(self) -> str:
+        """Which portion kernel to ask for: any (""), the CUDA-core one, or the fastest that adds a bias by distance."""
+        if self._cuda_cores_only():
+            return "simt"
+        return "biased" if self._has_distance_bias() else ""
+
+    def _has_distance_bias(self) -> bool:
+        return False
 
     def plan_key(self):
         if self.q_per_cta is None:
-            force = "simt" if self._cuda_cores_only() else ""
+            force = self._prefill_kernel()
             self.q_per_cta = ops.attention_prefill_q_per_cta(self.runtime.dtype, self.n_heads, self.n_kv, self.hd,
                                                               self.runtime.page_size, force)
         return ("paged_attention", self.q_per_cta, self.window)
@@ -221,7 +230,7 @@ class PagedAttention(Mixer):
         simt = self._cuda_cores_only()
         if plan["n_prefill"]:
             ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes, dist_bias=dist_bias,
-                                  force="simt" if simt else "", **common)
+                                  force=self._prefill_kernel(), **common)
         if plan["n_decode"]:
             items = None
             if not simt and ops.attention_decode_fast_ok(rt.dtype, self.n_heads, self.n_kv, self.hd, rt.page_size):

@@ -57,6 +57,9 @@ class ConvGatedAttention(PagedAttention):
         p = spec.params
         self.dk, self.dv = int(p["dim"]), int(p["vdim"])
         self.head_pad = (max(self.dk, self.dv) + 15) // 16 * 16
+        if runtime.dtype == torch.bfloat16:
+            # up to 128: the next head size the tensor-core attention kernels take
+            self.head_pad = next((n for n in (32, 64, 96, 128) if n >= self.head_pad), self.head_pad)
         if self.head_pad > 256:
             raise ValueError(f"conv_gated_attention: head sizes {self.dk} / {self.dv} exceed the 256 the kernels take")
         inner = PartSpec(spec.kind, {"hidden": p["hidden"], "n_heads": p["n_heads"], "n_kv_heads": p["n_kv_heads"],
@@ -135,6 +138,9 @@ class ConvGatedAttention(PagedAttention):
 
     def _distance_bias(self):
         return self.bias_table
+
+    def _has_distance_bias(self):
+        return bool(self.bias_rows)
 
     def flops_per_token(self) -> float:
         return 2.0 * self.hidden * (self.channels + self.g_cols + self.o_in)
