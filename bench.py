@@ -95,8 +95,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run this many of the configuration's layers (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
-    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex"])
-    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex: widths to run")
+    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex", "tabedra"])
+    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex or tabedra: widths to run")
     ap.add_argument("--marginal", action="store_true", help="marginal cost of each kernel family inside the decode step")
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="with --marginal: tokens each request holds")
     ap.add_argument("--marginal-prefill", action="store_true",
@@ -121,6 +121,8 @@ def main() -> int:
         return long_context_workload(args)
     if args.workload == "lokinex":
         return lokinex_workload(args)
+    if args.workload == "tabedra":
+        return lokinex_workload(args, design="tabedra")
 
     import numpy as np
     import torch
@@ -376,6 +378,37 @@ def lokinex_config(width: int) -> dict:
             "loop": {"start": 0, "stop": 4, "times": 2}}
 
 
+TABEDRA_WINDOW = 1024
+
+
+def tabedra_config(width: int) -> dict:
+    """A Tabedra model whose layers resemble real ones at this width: heads of 128 query/key and 128 value coordinates,
+    one key/value head per four query heads, convolutions of 4 taps, a sliding window of 1,024 keys with a distance-bias
+    table of 32 rows, four residual streams, 32 squared-ReLU experts as wide as the model with 4 per token and a shared
+    expert of twice that; eight layers, of which every second pair reads the keys and values of the layer before it."""
+    heads = width // 128
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4, "scale": 0.5,
+             "bias_max": float(TABEDRA_WINDOW), "bias_rows": 32, "mask": {"size": TABEDRA_WINDOW}}
+    moe = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": width}, "shared": {"ff": 2 * width}}
+    layers = []
+    for i in range(8):
+        m = dict(mixer)
+        if i % 4 >= 2:
+            m["kv_from"] = i - i % 4 + 1
+        layers.append({"type": "attention", "mixer": m, "mlp": moe})
+    return {"architecture": "Tabedra", "vocab": 32768, "width": width, "norm": {"eps": 1e-5}, "streams": 4,
+            "max_positions": 8192, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7919}},
+            "layers": layers}
+
+
+def qwen3_windowed(width: int) -> dict:
+    """The closest existing model for the Tabedra design: the Qwen3 decoder of :func:`qwen3_like` with the same sliding
+    window on every layer and as many key/value heads."""
+    heads = width // 128
+    return dict(qwen3_like(width), num_key_value_heads=max(1, heads // 4), use_sliding_window=True,
+                sliding_window=TABEDRA_WINDOW, max_window_layers=0, layer_types=["sliding_attention"] * 8)
+
+
 def qwen3_like(width: int) -> dict:
     """The closest existing model at equal size: as many layer runs (8), the same width, vocabulary and head size, a gated
     feed-forward with as many weights as the dense one above (3 matrices of 8/3 width against 2 of 4 width)."""
@@ -390,7 +423,8 @@ class OpTimer:
     NAMES = ("embed", "rmsnorm", "rmsnorm_add", "concat_embed", "short_conv", "block_linear", "gated_linear_recurrence",
              "gated_linear_recurrence_gates", "latent_kv_write", "relu_squared", "moe_route", "grouped_linear", "moe_combine",
              "grouped_gemm_mma", "attention_latent", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
-             "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand")
+             "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand", "embed_sum", "stream_layernorm",
+             "stream_update", "router_topk", "conv_norm_kv_write", "sigmoid_gate")
 
     def __init__(self):
         self.events, self.real = [], {}
@@ -430,10 +464,11 @@ class OpTimer:
         return {k: {"calls": v[0], "us": round(v[1], 1)} for k, v in sorted(out.items(), key=lambda kv: -kv[1][1])}
 
 
-def lokinex_workload(args) -> int:
-    """Prefill of one 2,048-token prompt and decode at batch 8 (2,048 tokens held each) of the Lokinex design at layer
-    sizes that resemble a real model's, beside the Qwen3 dense decoder at equal width, depth and vocabulary; device time
-    per kernel family of one prompt step and one decode step of each (eager steps with events around every launcher)."""
+def lokinex_workload(args, design: str = "lokinex") -> int:
+    """Prefill of one 2,048-token prompt and decode at batch 8 (2,048 tokens held each) of the Lokinex (or Tabedra) design
+    at layer sizes that resemble a real model's, beside the Qwen3 dense decoder at equal width, depth and vocabulary (for
+    Tabedra: with the same sliding window); device time per kernel family of one prompt step and one decode step of each
+    (eager steps with events around every launcher)."""
     import numpy as np
     import torch
     from rustingstrata_b200 import Engine
@@ -442,11 +477,12 @@ def lokinex_workload(args) -> int:
     pk = roofline.peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
     clocks = ClockSampler()
     clocks.start()
-    out = {"workload": "lokinex", "prompt_len": PROMPT, "batch": args.batch, "steps": args.steps, "dtype": "bf16",
+    pair = {"lokinex": (lokinex_config, qwen3_like), "tabedra": (tabedra_config, qwen3_windowed)}[design]
+    out = {"workload": design, "prompt_len": PROMPT, "batch": args.batch, "steps": args.steps, "dtype": "bf16",
            "data": "synthetic", "weights": "random N(0,0.02) bf16", "peaks": pk["source"], "sizes": {}}
     for width in [int(x) for x in args.sizes.split(",")]:
         rec = {}
-        for name, cfg in (("lokinex", lokinex_config(width)), ("qwen3", qwen3_like(width))):
+        for name, cfg in ((design, pair[0](width)), ("qwen3", pair[1](width))):
             V = cfg.get("vocab", cfg.get("vocab_size"))
             eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=args.batch * CONTEXT,
                          max_batch_tokens=PROMPT, max_seqs=args.batch)

@@ -48,6 +48,8 @@ struct TcParams {
     int n_q, n_kv, group, pack, pack_shift, tokens_per_cta;      // pack = 1 << pack_shift heads side by side in a tile
     int window;
     float scale_log2;
+    const float* bias_by_head; int n_dist;   // [n_q][n_dist] or null: entry min(query - key position, n_dist - 1) of the head's row,
+    float inv_scale;                         // times inv_scale = 1 / scale, joins the raw score (the scale is applied afterwards)
     int* status;
     int one_load_per_page;             // the 5-d map of the cache is in use (else 2-d loads of 8 keys x 64 dims)
     int out_by_tma;                    // the result has a tensor map: whole tiles are stored by the TMA unit
@@ -411,6 +413,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                         for (int i = 0; i < HK; ++i) x[i] = __uint_as_float(v[i]);          // raw scores: the scale goes into the exponent's FMA
                     }
+                    if (p.bias_by_head != nullptr) {
+                        // the bias tabulated by distance: key i of this part lies qpos - k0 - i back
+                        const float* brow = p.bias_by_head + (size_t)(I.head0 + (r & (p.pack - 1))) * p.n_dist;
+                        const int d0 = qpos - k0, last = p.n_dist - 1;
+#pragma unroll
+                        for (int i = 0; i < HK; ++i) x[i] = fmaf(__ldg(brow + min(max(d0 - i, 0), last)), p.inv_scale, x[i]);
+                    }
                     if (need_mask) {
                         // the keys a row sees are an interval: one subtraction and one unsigned comparison per score
                         const int first = max(key_lo, p.window > 0 ? qpos - p.window + 1 : 0) - k0;
@@ -676,8 +685,10 @@ RS_EXPORT int rs_attention_prefill_tc_q_per_cta(int n_q, int n_kv) { return ROWS
 RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows, void* out, long out_stride, const void* cache,
                                       long page_stride, int num_pages, int page_size, const int* block_table,
                                       int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
-                                      int n_q, int n_kv, int hd, int window, float scale, int* status, void* stream) {
+                                      int n_q, int n_kv, int hd, int window, float scale, const float* bias_by_head,
+                                      int n_dist, int* status, void* stream) {
     if (n_work <= 0) return 0;
+    if (bias_by_head != nullptr && (n_dist <= 0 || !(scale > 0.f))) return (int)cudaErrorInvalidValue;
     if (!rs_attention_prefill_tc_supported(n_q, n_kv, hd, page_size) || (q_stride % 8) || (out_stride % 8) || ((long)q & 15) ||
         ((long)out & 15) || ((long)cache & 15) || page_stride != (long)2 * n_kv * page_size * hd)
         return (int)cudaErrorInvalidValue;
@@ -688,6 +699,7 @@ RS_EXPORT int rs_attention_prefill_tc(const void* q, long q_stride, long q_rows,
     p.pack_shift = 0;
     while ((1 << p.pack_shift) < p.pack) ++p.pack_shift;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.bias_by_head = bias_by_head; p.n_dist = n_dist; p.inv_scale = bias_by_head != nullptr ? 1.0f / scale : 0.f;
     CUtensorMap mq, mkv, mo;
     int rc = cached_q_map(q, q_stride, q_rows, n_q, hd, p.pack, &mq);
     if (rc) return rc;

@@ -33,7 +33,68 @@ struct ConvKvParams {
     int* status;
 };
 
-__global__ void __launch_bounds__(128) conv_norm_kv_write_kernel(const ConvKvParams p) {
+// VEC neighbouring values starting at element i (a multiple of VEC when `vec`: one 4-, 8- or 16-byte access; else one by one)
+template <int VEC>
+__device__ __forceinline__ void load_run(const void* p, int dt, size_t i, bool vec, int n, float* v) {
+    if (vec) {
+        if (dt == RS_F32) {
+            const float* f = reinterpret_cast<const float*>(p) + i;
+            if constexpr (VEC == 1) { v[0] = f[0]; }
+            else if constexpr (VEC == 2) { const float2 a = *reinterpret_cast<const float2*>(f); v[0] = a.x; v[1] = a.y; }
+            else {
+#pragma unroll
+                for (int q = 0; q < VEC; q += 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(f + q);
+                    v[q] = a.x; v[q + 1] = a.y; v[q + 2] = a.z; v[q + 3] = a.w;
+                }
+            }
+        } else {
+            const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(p) + i;
+            if constexpr (VEC == 1) { v[0] = __bfloat162float(h[0]); }
+            else if constexpr (VEC == 2) { const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(h); v[0] = __low2float(a); v[1] = __high2float(a); }
+            else if constexpr (VEC == 4) {
+                const uint2 u = *reinterpret_cast<const uint2*>(h);
+                const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&u);
+                v[0] = __low2float(a[0]); v[1] = __high2float(a[0]); v[2] = __low2float(a[1]); v[3] = __high2float(a[1]);
+            } else {
+                const uint4 u = *reinterpret_cast<const uint4*>(h);
+                const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { v[2 * q] = __low2float(a[q]); v[2 * q + 1] = __high2float(a[q]); }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) v[q] = q < n ? load_any(p, dt, i + q) : 0.f;
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_run(void* p, int dt, size_t i, bool vec, int n, const float* v) {
+    if (vec && dt == RS_BF16 && VEC >= 2) {
+        __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p) + i;
+        if constexpr (VEC == 2) { *reinterpret_cast<__nv_bfloat162*>(h) = __floats2bfloat162_rn(v[0], v[1]); }
+        else if constexpr (VEC == 4) {
+            uint2 u;
+            __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&u);
+            a[0] = __floats2bfloat162_rn(v[0], v[1]); a[1] = __floats2bfloat162_rn(v[2], v[3]);
+            *reinterpret_cast<uint2*>(h) = u;
+        } else if constexpr (VEC == 8) {
+            uint4 u;
+            __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) a[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+            *reinterpret_cast<uint4*>(h) = u;
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) if (q < n) store_any(p, dt, i + q, v[q]);
+    }
+}
+
+// A warp per (token, head); a lane owns VEC neighbouring channels of the head (32 * VEC >= the padded head size).
+template <int VEC>
+__global__ void __launch_bounds__(128) conv_norm_kv_write_kernel(const ConvKvParams p, const int vec_ok) {
     const int lane = threadIdx.x & 31;
     const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
     const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -46,30 +107,33 @@ __global__ void __launch_bounds__(128) conv_norm_kv_write_kernel(const ConvKvPar
     if (item < p.n_q) { kind = 0; base = item * p.dk; width = p.dk; }
     else if (item < p.n_q + p.n_kv) { kind = 1; base = p.n_q * p.dk + (item - p.n_q) * p.dk; width = p.dk; }
     else { kind = 2; base = (p.n_q + p.n_kv) * p.dk + (item - p.n_q - p.n_kv) * p.dv; width = p.dv; }
-    float acc[MAX_PER_LANE];
-    float ss = 0.f;
+    const int d0 = lane * VEC;
+    const int n = min(max(width - d0, 0), VEC);        // this lane's channels inside the head
+    const bool vec = vec_ok && n == VEC;
+    float acc[VEC];
 #pragma unroll
-    for (int i = 0; i < MAX_PER_LANE; ++i) {
-        const int d = lane + 32 * i;
-        acc[i] = 0.f;
-        if (d >= width) continue;
-        const int c = base + d;
-        float a = 0.f;
+    for (int q = 0; q < VEC; ++q) acc[q] = 0.f;
+    if (n > 0) {
+        const int c = base + d0;
         if (p.taps <= 0) {
-            a = load_any(p.proj, p.dt, (size_t)t * p.proj_stride + c);
+            load_run<VEC>(p.proj, p.dt, (size_t)t * p.proj_stride + c, vec, n, acc);
         } else {
             for (int j = 0; j < p.taps; ++j) {
                 const int src = li - (p.taps - 1) + j;
-                const float x = src >= 0 ? load_any(p.proj, p.dt, (size_t)(row0 + src) * p.proj_stride + c)
-                                         : tail[(size_t)(p.taps - 1 + src) * p.C + c];
-                a = fmaf(load_any(p.w, p.w_dt, (size_t)j * p.C + c), x, a);
+                float x[VEC], w[VEC];
+                if (src >= 0) load_run<VEC>(p.proj, p.dt, (size_t)(row0 + src) * p.proj_stride + c, vec, n, x);
+                else load_run<VEC>(tail, RS_F32, (size_t)(p.taps - 1 + src) * p.C + c, vec, n, x);
+                load_run<VEC>(p.w, p.w_dt, (size_t)j * p.C + c, vec, n, w);
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) acc[q] = fmaf(w[q], x[q], acc[q]);
             }
         }
-        acc[i] = a;
-        ss = fmaf(a, a, ss);
     }
     float r = 1.0f;
     if (p.unit_norm && kind != 2) {
+        float ss = 0.f;
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) ss = fmaf(acc[q], acc[q], ss);       // channels beyond the head hold zero
         ss = warp_sum(ss);
         r = 1.0f / sqrtf(ss / (float)width + p.eps);
     }
@@ -88,10 +152,9 @@ __global__ void __launch_bounds__(128) conv_norm_kv_write_kernel(const ConvKvPar
         o = (size_t)page * p.page_stride + ((size_t)g * p.page_size + pos % p.page_size) * p.hdp + (kind == 2 ? p.v_offset : 0);
     }
 #pragma unroll
-    for (int i = 0; i < MAX_PER_LANE; ++i) {
-        const int d = lane + 32 * i;
-        if (d < p.hdp) store_any(dst, p.dt, o + d, d < width ? acc[i] * r : 0.f);
-    }
+    for (int q = 0; q < VEC; ++q) acc[q] *= r;
+    const int n_out = min(max(p.hdp - d0, 0), VEC);    // the padding behind the head is written too (zeros)
+    if (n_out > 0) store_run<VEC>(dst, p.dt, o + d0, vec_ok && n_out == VEC, n_out, acc);
 }
 
 // tail[i] <- the projected row at local index q_len - (taps - 1) + i: a row of this step, or a row the tail held.
@@ -112,17 +175,24 @@ __global__ void conv_tail_update_kernel(const void* __restrict__ proj, int dt, l
 }
 
 // out[t, h * dv + d] = a[t, h * hdp + d] * sigmoid(g[t, h * dv + d])    (g == null: a copy out of the padded rows)
+// A thread takes VEC neighbouring values of one head (dv a multiple of VEC, every row and head aligned for it).
+template <int VEC>
 __global__ void sigmoid_gate_kernel(const void* __restrict__ a, long a_stride, const void* __restrict__ g, long g_stride,
                                     void* __restrict__ out, long out_stride, int dt, int n_heads, int dv, int hdp,
                                     int n_tokens) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    const int W = n_heads * dv;
+    const int W = n_heads * dv / VEC;
     if (idx >= (long)n_tokens * W) return;
-    const int t = (int)(idx / W), c = (int)(idx % W);
+    const int t = (int)(idx / W), c = (int)(idx % W) * VEC;
     const int h = c / dv, d = c % dv;
-    float v = load_any(a, dt, (size_t)t * a_stride + (size_t)h * hdp + d);
-    if (g != nullptr) v *= 1.0f / (1.0f + expf(-load_any(g, dt, (size_t)t * g_stride + c)));
-    store_any(out, dt, (size_t)t * out_stride + c, v);
+    float v[VEC], z[VEC];
+    load_run<VEC>(a, dt, (size_t)t * a_stride + (size_t)h * hdp + d, true, VEC, v);
+    if (g != nullptr) {
+        load_run<VEC>(g, dt, (size_t)t * g_stride + c, true, VEC, z);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) v[q] *= 1.0f / (1.0f + expf(-z[q]));
+    }
+    store_run<VEC>(out, dt, (size_t)t * out_stride + c, true, VEC, v);
 }
 }  // namespace
 
@@ -141,7 +211,19 @@ RS_EXPORT int rs_conv_norm_kv_write(const void* proj, int dt, long proj_stride, 
                    block_table, table_stride, positions, pos_stride, seq_of_token, q_start, slots, n_tokens, status};
     cudaStream_t s = (cudaStream_t)stream;
     const long warps = (long)n_tokens * (n_q + (write_kv ? 2 * n_kv : 0));
-    conv_norm_kv_write_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(p);
+    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    const int vec_n = hdp <= 32 ? 1 : (hdp <= 64 ? 2 : (hdp <= 128 ? 4 : 8));
+    // vector accesses: every run of a lane starts at a multiple of its length, in every array it touches
+    const int es = dt == RS_F32 ? 4 : 2;
+    const bool vec_ok = dk % vec_n == 0 && dv % vec_n == 0 && hdp % vec_n == 0 && proj_stride % vec_n == 0 && C % vec_n == 0 &&
+                        q_stride % vec_n == 0 && tail_stride % vec_n == 0 && page_stride % vec_n == 0 &&
+                        ((size_t)proj % (vec_n * es)) == 0 && ((size_t)q_out % (vec_n * es)) == 0 &&
+                        ((size_t)cache % (vec_n * es)) == 0 && ((size_t)tails % (vec_n * 4)) == 0 &&
+                        ((size_t)w % (vec_n * (w_dt == RS_F32 ? 4 : 2))) == 0;
+    if (vec_n == 1) conv_norm_kv_write_kernel<1><<<blocks, 128, 0, s>>>(p, vec_ok);
+    else if (vec_n == 2) conv_norm_kv_write_kernel<2><<<blocks, 128, 0, s>>>(p, vec_ok);
+    else if (vec_n == 4) conv_norm_kv_write_kernel<4><<<blocks, 128, 0, s>>>(p, vec_ok);
+    else conv_norm_kv_write_kernel<8><<<blocks, 128, 0, s>>>(p, vec_ok);
     int e = rs_launch_result();
     if (e != 0 || taps <= 1) return e;
     const long n = (long)n_seqs * C;
@@ -154,8 +236,13 @@ RS_EXPORT int rs_sigmoid_gate(const void* a, long a_stride, const void* g, long 
                               int n_heads, int dv, int hdp, int n_tokens, void* stream) {
     if (n_tokens <= 0) return 0;
     const long n = (long)n_tokens * n_heads * dv;
-    sigmoid_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, a_stride, g, g_stride, out,
-                                                                                        out_stride, dt, n_heads, dv, hdp,
-                                                                                        n_tokens);
+    const int es = dt == RS_F32 ? 4 : 2;
+    const bool vec8 = dv % 8 == 0 && hdp % 8 == 0 && a_stride % 8 == 0 && g_stride % 8 == 0 && out_stride % 8 == 0 &&
+                      ((size_t)a % (8 * es)) == 0 && ((size_t)g % (8 * es)) == 0 && ((size_t)out % (8 * es)) == 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (vec8) sigmoid_gate_kernel<8><<<(unsigned)((n / 8 + 255) / 256), 256, 0, s>>>(a, a_stride, g, g_stride, out, out_stride,
+                                                                                   dt, n_heads, dv, hdp, n_tokens);
+    else sigmoid_gate_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, a_stride, g, g_stride, out, out_stride, dt,
+                                                                          n_heads, dv, hdp, n_tokens);
     return rs_launch_result();
 }

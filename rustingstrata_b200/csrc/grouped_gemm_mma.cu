@@ -21,7 +21,7 @@ struct GroupedMmaParams {
     void* out; int out_dt; long out_stride; long out_expert_cols;  // expert e writes columns from e * out_expert_cols
     const int* order; const int* tiles; const int* n_tiles;        // tiles == null: every expert takes all dense_rows rows
     int dense_rows, tiles_per_expert;
-    int K, gated;
+    int K, gated;                                                  // gated: 0 plain; 1 SiLU(gate) * up of alternating rows; 2 plain, then max(., 0)^2
 };
 
 // BM x BN: the CTA's tile; WM x WN warps, each owning (BM / WM) x (BN / WN) of it.  64 x 64 with 2 x 2 warps where an
@@ -134,7 +134,11 @@ __global__ void __launch_bounds__(WM * WN * 32) grouped_gemm_mma_kernel(const Gr
                     if (gn < p.w_rows) c0 += load_any(p.bias, p.bias_dt, (size_t)e * p.w_rows + gn);
                     if (gn + 1 < p.w_rows) c1 += load_any(p.bias, p.bias_dt, (size_t)e * p.w_rows + gn + 1);
                 }
-                if (p.gated) {
+                if (p.gated == 2) {
+                    c0 = fmaxf(c0, 0.f); c0 *= c0;
+                    c1 = fmaxf(c1, 0.f); c1 *= c1;
+                }
+                if (p.gated == 1) {
                     if (gn + 1 < p.w_rows) {
                         const float v = silu_mul_fast(c0, c1);
                         const size_t o = (size_t)pr * p.out_stride + (size_t)e * p.out_expert_cols + (gn >> 1);
@@ -167,7 +171,7 @@ RS_EXPORT int rs_grouped_gemm_mma(const void* a, long a_stride, int a_div, const
                                   void* out, int out_dt, long out_stride, const int* order, const int* tiles,
                                   const int* n_tiles, int max_tiles, int K, int gated, int large, void* stream) {
     if (max_tiles <= 0 || w_rows <= 0) return 0;
-    if (K <= 0 || K % 8 || a_stride % 8 || w_expert_stride % 8 || ((size_t)a & 15) || ((size_t)w & 15) || (gated && w_rows % 2))
+    if (K <= 0 || K % 8 || a_stride % 8 || w_expert_stride % 8 || ((size_t)a & 15) || ((size_t)w & 15) || (gated == 1 && w_rows % 2) || gated < 0 || gated > 2)
         return (int)cudaErrorInvalidValue;
     GroupedMmaParams p{a, RS_BF16, a_stride, a_div, 0, (const __nv_bfloat16*)w, w_expert_stride, w_rows, nullptr, 0, out, out_dt,
                        out_stride, 0, order, tiles, n_tiles, 0, 1, K, gated};

@@ -340,7 +340,7 @@ def bf16lib():
                                                   c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_attention_prefill_tc.argtypes = [c_void_p, c_long, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                c_int, c_float, c_void_p, c_void_p]
+                                                c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]
         lib.rs_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_attention_prefill_tc_q_per_cta.argtypes = [c_int, c_int]
         lib.rs_grouped_gemm_mma.argtypes = [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_void_p,
@@ -791,10 +791,14 @@ def _partial_slots(partial: Optional[torch.Tensor], total_splits: int, n_q: int,
 def attention_prefill_kernel(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int, force: str = "") -> str:
     """Which kernel ``attention_prefill`` runs for this shape: "tc" (tcgen05, head 64/128, page size a power of
     two from 8 to 128), "mma" (mma.sync, head 32/64/96/128) or "simt" (everything else, and float32).  ``force``
-    names one; "biased" asks for the fastest kernel that adds a bias tabulated by distance ("mma", else "simt")."""
-    if force == "biased":
-        if dtype == torch.bfloat16 and bf16lib().rs_attention_prefill_bf16_supported(n_q, n_kv, head_dim):
-            return "mma"
+    names one; "biased" asks for the fastest kernel that adds a bias tabulated by distance (all three do; "biased_mma"
+    leaves the tcgen05 kernel out)."""
+    if force in ("biased", "biased_mma"):
+        if dtype == torch.bfloat16:
+            if force == "biased" and bf16lib().rs_attention_prefill_tc_supported(n_q, n_kv, head_dim, page_size):
+                return "tc"
+            if bf16lib().rs_attention_prefill_bf16_supported(n_q, n_kv, head_dim):
+                return "mma"
         return "simt"
     if force:
         return force
@@ -826,17 +830,21 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
                       q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_q: int, n_kv: int,
                       head_dim: int, page_size: int, window: int, scale: float, status: torch.Tensor,
                       force: str = "", slopes: Optional[torch.Tensor] = None, one_plane: bool = False,
-                      dist_bias: Optional[torch.Tensor] = None) -> None:
+                      dist_bias: Optional[torch.Tensor] = None, dist_bias_by_head: Optional[torch.Tensor] = None) -> None:
     """Attention of prompt portions; ``work`` lists (sequence, first query) tiles of ``attention_prefill_q_per_cta``
     tokens.  tcgen05 kernel (csrc/attention_prefill_tc.cu), mma.sync kernel (csrc/attention_prefill_mma.cu) or
-    CUDA cores, whichever takes the shape; ``force`` names one.  Score biases (``slopes``) are the CUDA-core kernel's."""
+    CUDA cores, whichever takes the shape; ``force`` names one.  Score slopes are the CUDA-core kernel's; a bias
+    tabulated by distance (``dist_bias`` [distances, heads], see :func:`attention_simt`) is added by all three, the
+    tcgen05 kernel reading its transpose ``dist_bias_by_head`` [heads, distances] (and wanting a positive scale)."""
     kind = attention_prefill_kernel(q.dtype, n_q, n_kv, head_dim, page_size, force)
     if (slopes is not None or one_plane) and kind != "simt":
         raise KernelError("attention_prefill: only the CUDA-core kernel (force='simt') adds score slopes or reads a "
                           "one-plane cache")
     if dist_bias is not None and kind == "tc":
-        raise KernelError("attention_prefill: a bias tabulated by distance is added by the mma.sync and CUDA-core kernels "
-                          "(force='biased')")
+        if dist_bias_by_head is None or dist_bias_by_head.dtype != torch.float32 or not dist_bias_by_head.is_contiguous() \
+                or tuple(dist_bias_by_head.shape) != (n_q, dist_bias.shape[0]) or not dist_bias_by_head.is_cuda or scale <= 0:
+            raise KernelError(f"attention_prefill: the tcgen05 kernel reads the bias as contiguous float32 [{n_q}, distances] "
+                              f"and wants a positive scale")
     if kind == "simt":
         attention_simt(q, out, cache, block_table, q_start, kv_len, work, n_work, n_q, n_kv, head_dim, page_size, window,
                        scale, False, status, slopes=slopes, one_plane=one_plane, dist_bias=dist_bias)
@@ -856,7 +864,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
         _check(fn(
             _ptr(q), q.stride(0), min(q.shape[0], out.shape[0]), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0],
             page_size, _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_q, n_kv,
-            head_dim, int(window), float(scale), _ptr(status), _stream()), "attention_prefill_" + kind)
+            head_dim, int(window), float(scale), _ptr(dist_bias_by_head if dist_bias is not None else None),
+            0 if dist_bias is None else dist_bias.shape[0], _ptr(status), _stream()), "attention_prefill_" + kind)
         return
     _check(bf16lib().rs_attention_prefill_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
@@ -1271,12 +1280,16 @@ GROUPED_ROWS_LARGE = 128      # row tile of the tensor-core grouped product's fo
 
 
 def grouped_gemm_mma(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: torch.Tensor, order: torch.Tensor,
-                     tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, large: bool = False) -> None:
+                     tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, gated: bool, large: bool = False,
+                     relu2: bool = False) -> None:
     """The grouped product of :func:`grouped_linear` on the tensor cores (csrc/grouped_gemm_mma.cu), for the row tiles
     that ``moe_route`` lists: of ``GROUPED_ROWS_TILED`` rows (64 x 64 tiles, for few rows per expert), or with ``large`` of
     ``GROUPED_ROWS_LARGE`` (128 x 128 tiles, for prompt portions).  ``gated``: the rows of every expert's matrix alternate
-    gate, up and out = SiLU(gate) * up has half as many columns as the matrix has rows."""
+    gate, up and out = SiLU(gate) * up has half as many columns as the matrix has rows.  ``relu2`` (plain products only):
+    out = max(a W.T, 0)^2."""
     _cuda(a, weight, out, order, tiles, n_tiles)
+    if gated and relu2:
+        raise KernelError("grouped_gemm_mma: the squared ReLU follows a plain product, not a gated one")
     _rows_contiguous(out, "grouped_gemm_mma out")
     if not grouped_gemm_mma_ok(a, weight):
         raise KernelError("grouped_gemm_mma: bfloat16 operands with 16-byte aligned rows and k a multiple of 8")
@@ -1289,7 +1302,7 @@ def grouped_gemm_mma(a: torch.Tensor, a_div: int, weight: torch.Tensor, out: tor
         raise KernelError("grouped_gemm_mma: the compiled kernel's row tiles differ from the launcher's")
     _check(bf16lib().rs_grouped_gemm_mma(_ptr(a), a.stride(0), a_div, _ptr(weight), weight.stride(0), rows, _ptr(out),
                                          dtype_code(out), out.stride(0), _ptr(order), _ptr(tiles), _ptr(n_tiles), max_tiles,
-                                         K, 1 if gated else 0, 1 if large else 0, _stream()), "grouped_gemm_mma")
+                                         K, 1 if gated else (2 if relu2 else 0), 1 if large else 0, _stream()), "grouped_gemm_mma")
 
 
 def moe_combine(pair_out: torch.Tensor, top: int, weight: float, out: torch.Tensor, n_tokens: int,

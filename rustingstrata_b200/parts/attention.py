@@ -29,6 +29,7 @@ from .base import CallInfo, HostBatch, Mixer, StepContext
 from .registry import register_part
 from .spec import CacheNeed, TensorNeed
 
+BIASED_TCGEN05 = True    # whether attention with a bias tabulated by distance may take the tcgen05 portion kernel
 SPLIT_KEYS = 128     # keys per split of the decode form; fixed so a position's reduction order never changes
 SPLIT_BUCKET = 8     # captured steps round the number of splits launched up to a multiple of this
 
@@ -147,7 +148,9 @@ class PagedAttention(Mixer):
         """Which portion kernel to ask for: any (""), the CUDA-core one, or the fastest that adds a bias by distance."""
         if self._cuda_cores_only():
             return "simt"
-        return "biased" if self._has_distance_bias() else ""
+        if not self._has_distance_bias():
+            return ""
+        return "biased" if self.scale > 0 and BIASED_TCGEN05 else "biased_mma"
 
     def _has_distance_bias(self) -> bool:
         return False
@@ -230,6 +233,7 @@ class PagedAttention(Mixer):
         simt = self._cuda_cores_only()
         if plan["n_prefill"]:
             ops.attention_prefill(work=plan["prefill_work"], n_work=plan["n_prefill"], slopes=slopes, dist_bias=dist_bias,
+                                  dist_bias_by_head=getattr(self, "bias_table_by_head", None),
                                   force=self._prefill_kernel(), **common)
         if plan["n_decode"]:
             items = None

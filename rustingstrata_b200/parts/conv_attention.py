@@ -10,7 +10,8 @@ request are its state); every q and k head is divided by sqrt(mean square + eps)
 with bucket(n) = n below half the table's rows B/2, then evenly spaced in log(n) so that distance ``bias_max`` reaches
 the last row: B/2 + floor(log(n / (B/2)) / log(bias_max / (B/2)) * (B - B/2)), capped at B - 1.  Softmax over the
 visible keys, the joined heads times sigmoid(W_g h), then W_o.  Keys and values may have different sizes; the cache and
-the attention kernels see heads padded with zeros to a common multiple of 16.  A call that reads another call's cache
+the attention kernels see heads padded with zeros to a common size (a multiple of 16; in the bfloat16 engine the next
+size its tensor-core attention kernels take).  A call that reads another call's cache
 projects and convolves queries only.
 
 The work lists, split form and workspaces are those of :class:`~rustingstrata_b200.parts.attention.PagedAttention`;
@@ -90,7 +91,7 @@ class ConvGatedAttention(PagedAttention):
         rt = runtime
         rt.scratch("conv_proj", rt.max_batch_tokens, self.channels + self.g_cols)
         rt.scratch("gated_heads", rt.max_batch_tokens, self.o_in)
-        self.w_in = self.w_conv = self.bias_table = None
+        self.w_in = self.w_conv = self.bias_table = self.bias_table_by_head = None
 
     # ---------------------------------------------------------------- weights
     def tensor_needs(self):
@@ -128,6 +129,7 @@ class ConvGatedAttention(PagedAttention):
             n = max(1, min(reach, int(math.ceil(self.bias_max)) + 1))
             rows = torch.from_numpy(distance_rows(self.bias_rows, self.bias_max, n)).to(tensors[t["rel"]].device)
             self.bias_table = tensors[t["rel"]].to(torch.float32)[rows].contiguous()
+            self.bias_table_by_head = self.bias_table.t().contiguous()      # the tcgen05 kernel's threads walk one head's row
 
     # ---------------------------------------------------------------- state
     def cache_need(self):

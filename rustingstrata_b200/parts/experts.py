@@ -262,8 +262,7 @@ class RoutedMoE(FeedForward):
         ops.router_topk(logits, self.correction, top, T, choice, weights, ctx.status)
         ops.moe_route(None, choice.view(T, top), self.n_experts, T, rows, order, tiles, n_tiles, ctx.status)
         if tensor_cores:
-            ops.grouped_gemm_mma(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, large=large)
-            ops.relu_squared(act, act, pairs)
+            ops.grouped_gemm_mma(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, large=large, relu2=True)
             ops.grouped_gemm_mma(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, large=large)
         else:
             ops.grouped_linear(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, small=small, relu2=True)
