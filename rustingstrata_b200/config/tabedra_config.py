@@ -77,7 +77,10 @@ class TabedraConfig:
         bigram = None
         if isinstance(big, Mapping):
             w = where + " embedding.bigram"
-            bigram = (_require(big, "buckets", int, w), _require(big, "mul_prev", int, w), _require(big, "mul_cur", int, w))
+            for key in ("mul_prev", "mul_cur"):
+                if isinstance(big.get(key), bool) or not isinstance(big.get(key), int):
+                    raise ConfigError(f"{w}: key '{key}' must be an integer, got {big.get(key)!r}")
+            bigram = (_require(big, "buckets", int, w), int(big["mul_prev"]), int(big["mul_cur"]))
         raw_layers = d.get("layers")
         if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
             raise ConfigError(f"{where}: 'layers' must list at least one layer")

@@ -46,6 +46,7 @@ __global__ void embed_sum_kernel(const EmbedSumParams p) {
             int prev = t > p.q_start[s] ? p.ids[t - 1] : p.prev_state[(size_t)p.slots[s] * p.state_stride];
             if (prev < 0 || prev >= p.V) prev = 0;
             row = ((long)prev * p.mul_prev + (long)id * p.mul_cur) % (long)p.buckets;
+            if (row < 0) row += p.buckets;                     // the remainder of a floored division, also for negative factors
         }
     }
     if (p.pos != nullptr && (place < 0 || place >= p.n_pos)) {
