@@ -178,7 +178,7 @@ def main(argv=None) -> int:
     if argv and argv[0] == "replay":          # everything behind the word belongs to trace replay's own parser
         from .replay import main as replay_main
         return replay_main(argv[1:])
-    ap = argparse.ArgumentParser(prog="rustingstrata_b200", description="B200 inference engine (Qwen3 dense and Lokinex decoders)")
+    ap = argparse.ArgumentParser(prog="rustingstrata_b200", description="B200 inference engine (Qwen3 dense, Lokinex and Tabedra decoders)")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="generation (greedy unless --temp)")
     _engine_flags(g)

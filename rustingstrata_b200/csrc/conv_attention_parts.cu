@@ -92,14 +92,16 @@ __device__ __forceinline__ void store_run(void* p, int dt, size_t i, bool vec, i
     }
 }
 
-// A warp per (token, head); a lane owns VEC neighbouring channels of the head (32 * VEC >= the padded head size).
+// A warp per (token, head); a lane owns VEC neighbouring channels of the head (32 * VEC >= the padded head size).  The
+// warps of a CTA take neighbouring tokens of one head: the rows that the taps of one token read are the rows its
+// neighbours read, so all but the first read of a row is served by the SM's own cache.
 template <int VEC>
-__global__ void __launch_bounds__(128) conv_norm_kv_write_kernel(const ConvKvParams p, const int vec_ok) {
+__global__ void __launch_bounds__(256) conv_norm_kv_write_kernel(const ConvKvParams p, const int vec_ok) {
     const int lane = threadIdx.x & 31;
     const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
-    const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (wid >= (long)p.n_tokens * items) return;
-    const int t = (int)(wid / items), item = (int)(wid % items);
+    const unsigned wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // the launcher keeps tokens * items below 2^31
+    if (wid >= (unsigned)p.n_tokens * (unsigned)items) return;
+    const int item = (int)(wid / (unsigned)p.n_tokens), t = (int)(wid - (unsigned)item * (unsigned)p.n_tokens);
     const int s = p.seq_of_token[t];
     const int row0 = p.q_start[s], li = t - row0;
     const float* tail = p.tail + (size_t)p.slots[s] * p.tail_stride;
@@ -211,7 +213,8 @@ RS_EXPORT int rs_conv_norm_kv_write(const void* proj, int dt, long proj_stride, 
                    block_table, table_stride, positions, pos_stride, seq_of_token, q_start, slots, n_tokens, status};
     cudaStream_t s = (cudaStream_t)stream;
     const long warps = (long)n_tokens * (n_q + (write_kv ? 2 * n_kv : 0));
-    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    if (warps >= (1L << 31)) return (int)cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
     const int vec_n = hdp <= 32 ? 1 : (hdp <= 64 ? 2 : (hdp <= 128 ? 4 : 8));
     // vector accesses: every run of a lane starts at a multiple of its length, in every array it touches
     const int es = dt == RS_F32 ? 4 : 2;
@@ -220,10 +223,10 @@ RS_EXPORT int rs_conv_norm_kv_write(const void* proj, int dt, long proj_stride, 
                         ((size_t)proj % (vec_n * es)) == 0 && ((size_t)q_out % (vec_n * es)) == 0 &&
                         ((size_t)cache % (vec_n * es)) == 0 && ((size_t)tails % (vec_n * 4)) == 0 &&
                         ((size_t)w % (vec_n * (w_dt == RS_F32 ? 4 : 2))) == 0;
-    if (vec_n == 1) conv_norm_kv_write_kernel<1><<<blocks, 128, 0, s>>>(p, vec_ok);
-    else if (vec_n == 2) conv_norm_kv_write_kernel<2><<<blocks, 128, 0, s>>>(p, vec_ok);
-    else if (vec_n == 4) conv_norm_kv_write_kernel<4><<<blocks, 128, 0, s>>>(p, vec_ok);
-    else conv_norm_kv_write_kernel<8><<<blocks, 128, 0, s>>>(p, vec_ok);
+    if (vec_n == 1) conv_norm_kv_write_kernel<1><<<blocks, 256, 0, s>>>(p, vec_ok);
+    else if (vec_n == 2) conv_norm_kv_write_kernel<2><<<blocks, 256, 0, s>>>(p, vec_ok);
+    else if (vec_n == 4) conv_norm_kv_write_kernel<4><<<blocks, 256, 0, s>>>(p, vec_ok);
+    else conv_norm_kv_write_kernel<8><<<blocks, 256, 0, s>>>(p, vec_ok);
     int e = rs_launch_result();
     if (e != 0 || taps <= 1) return e;
     const long n = (long)n_seqs * C;
