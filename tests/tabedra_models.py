@@ -72,7 +72,7 @@ CONFIGS = {
         (attn(4, 2, 64, 64, conv=4, bias_max=100.0, rows=32, window=128), moe(8, 2, 64, shared=96)),
         (attn(4, 1, 64, 64, conv=None, bias_max=300.0, rows=20, window=None), moe(8, 4, 32)),
         (attn(4, 2, 64, 64, conv=2, bias_max=100.0, rows=32, window=200, kv_from=0), None),
-    ], streams=None, bigram=(509, 3, 11)),
+    ], streams=None, bigram=(251, 3, 11)),
 }
 
 
