@@ -95,7 +95,10 @@ __device__ __forceinline__ void store_run(void* p, int dt, size_t i, bool vec, i
 // A warp per (token, head); a lane owns VEC neighbouring channels of the head (32 * VEC >= the padded head size).  The
 // warps of a CTA take neighbouring tokens of one head: the rows that the taps of one token read are the rows its
 // neighbours read, so all but the first read of a row is served by the SM's own cache.
-template <int VEC>
+// FAST: bfloat16 rows and weights with every run aligned (vec_ok): loads without run-time type or alignment branches, and
+// for a token whose taps all read rows of this step, a loop the compiler can unroll with its loads issued together
+// (one tap's load after the other's arithmetic made the kernel wait out the memory latency once per tap).
+template <int VEC, bool FAST>
 __global__ void __launch_bounds__(256) conv_norm_kv_write_kernel(const ConvKvParams p, const int vec_ok) {
     const int lane = threadIdx.x & 31;
     const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
@@ -119,6 +122,16 @@ __global__ void __launch_bounds__(256) conv_norm_kv_write_kernel(const ConvKvPar
         const int c = base + d0;
         if (p.taps <= 0) {
             load_run<VEC>(p.proj, p.dt, (size_t)t * p.proj_stride + c, vec, n, acc);
+        } else if (FAST && li >= p.taps - 1) {
+            const size_t r0 = (size_t)(t - (p.taps - 1)) * p.proj_stride + c;
+#pragma unroll 4
+            for (int j = 0; j < p.taps; ++j) {
+                float x[VEC], w[VEC];
+                load_run<VEC>(p.proj, RS_BF16, r0 + (size_t)j * p.proj_stride, true, VEC, x);
+                load_run<VEC>(p.w, RS_BF16, (size_t)j * p.C + c, true, VEC, w);
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) acc[q] = fmaf(w[q], x[q], acc[q]);
+            }
         } else {
             for (int j = 0; j < p.taps; ++j) {
                 const int src = li - (p.taps - 1) + j;
@@ -223,10 +236,18 @@ RS_EXPORT int rs_conv_norm_kv_write(const void* proj, int dt, long proj_stride, 
                         ((size_t)proj % (vec_n * es)) == 0 && ((size_t)q_out % (vec_n * es)) == 0 &&
                         ((size_t)cache % (vec_n * es)) == 0 && ((size_t)tails % (vec_n * 4)) == 0 &&
                         ((size_t)w % (vec_n * (w_dt == RS_F32 ? 4 : 2))) == 0;
-    if (vec_n == 1) conv_norm_kv_write_kernel<1><<<blocks, 256, 0, s>>>(p, vec_ok);
-    else if (vec_n == 2) conv_norm_kv_write_kernel<2><<<blocks, 256, 0, s>>>(p, vec_ok);
-    else if (vec_n == 4) conv_norm_kv_write_kernel<4><<<blocks, 256, 0, s>>>(p, vec_ok);
-    else conv_norm_kv_write_kernel<8><<<blocks, 256, 0, s>>>(p, vec_ok);
+    const bool fast = vec_ok && dt == RS_BF16 && (taps <= 0 || w_dt == RS_BF16);
+    if (fast) {
+        if (vec_n == 1) conv_norm_kv_write_kernel<1, true><<<blocks, 256, 0, s>>>(p, vec_ok);
+        else if (vec_n == 2) conv_norm_kv_write_kernel<2, true><<<blocks, 256, 0, s>>>(p, vec_ok);
+        else if (vec_n == 4) conv_norm_kv_write_kernel<4, true><<<blocks, 256, 0, s>>>(p, vec_ok);
+        else conv_norm_kv_write_kernel<8, true><<<blocks, 256, 0, s>>>(p, vec_ok);
+    } else {
+        if (vec_n == 1) conv_norm_kv_write_kernel<1, false><<<blocks, 256, 0, s>>>(p, vec_ok);
+        else if (vec_n == 2) conv_norm_kv_write_kernel<2, false><<<blocks, 256, 0, s>>>(p, vec_ok);
+        else if (vec_n == 4) conv_norm_kv_write_kernel<4, false><<<blocks, 256, 0, s>>>(p, vec_ok);
+        else conv_norm_kv_write_kernel<8, false><<<blocks, 256, 0, s>>>(p, vec_ok);
+    }
     int e = rs_launch_result();
     if (e != 0 || taps <= 1) return e;
     const long n = (long)n_seqs * C;
