@@ -12,7 +12,7 @@
 #include <math.h>
 
 namespace {
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
 __device__ __forceinline__ void store_any(void* p, int dt, size_t i, float v) {
     if (dt == RS_F32) reinterpret_cast<float*>(p)[i] = v;
@@ -101,7 +101,7 @@ __global__ void stream_layernorm_kernel(const StreamNormParams p) {
     __shared__ float scratch[33];
     __shared__ float cf[MAX_STREAMS];
     const int r = blockIdx.x;
-    if (threadIdx.x < p.S) cf[threadIdx.x] = p.coef != nullptr ? load_any(p.coef, p.coef_dt, threadIdx.x) : 1.0f;
+    for (int i = threadIdx.x; i < p.S; i += blockDim.x) cf[i] = p.coef != nullptr ? load_any(p.coef, p.coef_dt, i) : 1.0f;
     __syncthreads();
     const float* xr = p.x + (size_t)(p.rows != nullptr ? p.rows[r] : r) * p.x_stride;
     for (int i = threadIdx.x; i < p.D; i += blockDim.x) {
@@ -122,32 +122,34 @@ struct StreamUpdateParams {
     int S, D;
 };
 
+// MS: the least of 1, 2, 4, 8, 16 that holds the S streams (the loops over streams are unrolled to it)
+template <int MS>
 __global__ void stream_update_kernel(const StreamUpdateParams p) {
     extern __shared__ float u[];
     __shared__ float scratch[33];
     __shared__ float mx[MAX_STREAMS * MAX_STREAMS], oc[MAX_STREAMS], cf[MAX_STREAMS];
     const int r = blockIdx.x, S = p.S;
-    if (threadIdx.x < S * S) mx[threadIdx.x] = load_any(p.mix, p.mix_dt, threadIdx.x);
-    if (threadIdx.x < S) {
-        oc[threadIdx.x] = load_any(p.outc, p.outc_dt, threadIdx.x);
-        cf[threadIdx.x] = p.next.coef != nullptr ? load_any(p.next.coef, p.next.coef_dt, threadIdx.x) : 1.0f;
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) mx[i] = load_any(p.mix, p.mix_dt, i);
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+        oc[i] = load_any(p.outc, p.outc_dt, i);
+        cf[i] = p.next.coef != nullptr ? load_any(p.next.coef, p.next.coef_dt, i) : 1.0f;
     }
     __syncthreads();
     float* xr = p.x + (size_t)r * p.x_stride;
     const float* yr = p.y + (size_t)r * p.y_stride;
     const bool norm = p.next.out != nullptr;
     for (int i = threadIdx.x; i < p.D; i += blockDim.x) {
-        float xs[MAX_STREAMS];
+        float xs[MS];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * p.D + i] : 0.f;
+        for (int s = 0; s < MS; ++s) xs[s] = s < S ? xr[(size_t)s * p.D + i] : 0.f;
         const float yv = yr[i];
         float acc = 0.f;
 #pragma unroll
-        for (int t = 0; t < MAX_STREAMS; ++t) {
+        for (int t = 0; t < MS; ++t) {
             if (t >= S) break;
             float nx = 0.f;
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; ++s)
+            for (int s = 0; s < MS; ++s)
                 if (s < S) nx = fmaf(mx[s * S + t], xs[s], nx);
             nx = fmaf(oc[t], yv, nx);
             xr[(size_t)t * p.D + i] = nx;
@@ -249,8 +251,14 @@ RS_EXPORT int rs_stream_update(float* x, long x_stride, const float* y, long y_s
     p.x = x; p.x_stride = x_stride; p.y = y; p.y_stride = y_stride; p.mix = mix; p.mix_dt = mix_dt; p.outc = outc;
     p.outc_dt = outc_dt; p.S = S; p.D = D;
     p.next = StreamNormParams{x, x_stride, nullptr, coef, coef_dt, w, w_dt, b, b_dt, eps, out, out_dt, out_stride, S, D};
-    const int threads = norm_threads(D) < 64 ? 64 : norm_threads(D);       // at least S * S threads load the coefficients
-    stream_update_kernel<<<n_rows, threads, out != nullptr ? (size_t)D * sizeof(float) : 0, (cudaStream_t)stream>>>(p);
+    const int threads = S > 8 && norm_threads(D) > 256 ? 256 : norm_threads(D);     // the widest form holds 16 streams in registers
+    const size_t smem = out != nullptr ? (size_t)D * sizeof(float) : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (S == 1) stream_update_kernel<1><<<n_rows, threads, smem, st>>>(p);
+    else if (S == 2) stream_update_kernel<2><<<n_rows, threads, smem, st>>>(p);
+    else if (S <= 4) stream_update_kernel<4><<<n_rows, threads, smem, st>>>(p);
+    else if (S <= 8) stream_update_kernel<8><<<n_rows, threads, smem, st>>>(p);
+    else stream_update_kernel<16><<<n_rows, threads, smem, st>>>(p);
     return rs_launch_result();
 }
 

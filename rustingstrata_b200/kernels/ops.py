@@ -1364,7 +1364,7 @@ def streamlib():
     return _streamlib
 
 
-MAX_STREAMS = 8            # residual streams the stream kernels take
+MAX_STREAMS = 16           # residual streams the stream kernels take
 MAX_STREAM_WIDTH = 12288   # widest row they hold in shared memory
 
 

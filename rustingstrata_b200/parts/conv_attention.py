@@ -69,8 +69,8 @@ class ConvGatedAttention(PagedAttention):
         super().__init__(inner, runtime, position)
         self.spec = spec
         self.taps = int(p.get("taps") or 0)
-        if self.taps > 17:
-            raise ValueError(f"conv_gated_attention: {self.taps} taps (up to 17 are supported)")
+        if self.taps > 64:
+            raise ValueError(f"conv_gated_attention: {self.taps} taps (up to 64 are supported)")
         self.unit_norm = bool(p.get("unit_norm", True))
         self.eps = float(p.get("eps", 0.0))
         self.gate = bool(p.get("gate", True))

@@ -81,6 +81,7 @@ ONE_LAYER = {
                                     streams=None, bigram=None),
     "attention_padded_heads": M.config(97, 72, [(M.attn(5, 1, 20, 36, conv=2, rows=10, bias_max=44.0), None)], streams=None, bigram=None),
     "bigram_embedding": M.config(97, 64, [(M.attn(2, 1, 16, 16, conv=None, rows=4, bias_max=9.0), None)], streams=None, bigram=(23, 5, 3)),
+    "streams_nine_taps_twenty": M.config(97, 64, [(M.attn(2, 1, 16, 16, conv=20, rows=4, bias_max=9.0), None)], streams=9, bigram=None),
     "streams_four": M.config(97, 64, [(M.attn(2, 1, 16, 16, conv=None, rows=4, bias_max=9.0), None)], streams=4, bigram=None),
     "experts_top2_shared": M.config(97, 64, [(M.attn(2, 1, 16, 16, conv=None), M.moe(6, 2, 24, shared=40))], streams=None, bigram=None),
     "experts_top1_unshared": M.config(97, 64, [(M.attn(2, 1, 16, 16, conv=None), M.moe(4, 1, 40))], streams=2, bigram=None),
