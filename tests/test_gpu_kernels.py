@@ -240,20 +240,23 @@ def test_qk_without_norm_without_rope_and_without_kv():
 
 
 # ------------------------------------------------------------------------------- attention
-def ref_attention(q, keys, vals, q_pos, n_kv, window, scale):
-    """q [nq, hd] at position q_pos over keys/vals [L, nkv, hd] (float64): src/model.rs:778-791."""
+def ref_attention(q, keys, vals, q_pos, n_kv, window, scale, bias=None):
+    """q [nq, hd] at position q_pos over keys/vals [L, nkv, hd] (float64): src/model.rs:778-791.  ``bias`` [distances,
+    nq] float64: row min(distance, last) joins the scaled scores."""
     nq = q.shape[0]
     lo = max(0, q_pos - window + 1) if window else 0
     out = torch.zeros_like(q)
     for h in range(nq):
         g = h // (nq // n_kv)
         s = (keys[lo:q_pos + 1, g] @ q[h]) * scale
+        if bias is not None:
+            s = s + bias[torch.clamp(q_pos - torch.arange(lo, q_pos + 1), max=bias.shape[0] - 1), h]
         p = torch.softmax(s, 0)
         out[h] = p @ vals[lo:q_pos + 1, g]
     return out
 
 
-def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None, force_simt=False, prefill=""):
+def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=None, force_simt=False, prefill="", bias=None):
     """seqs: list of (kv_len, q_len).  Builds a shuffled paged cache, runs the kernels the mixer would
     run (split form for one query, tile form otherwise) and returns (got, want) [T, n_q, hd]."""
     o = ops()
@@ -293,8 +296,11 @@ def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=
     st = status()
     common = dict(q=qd, out=out, cache=cache, block_table=perm.to(DEV), q_start=dev(q_start), kv_len=dev(kv_lens),
                   n_q=n_q, n_kv=n_kv, head_dim=hd, page_size=page, window=window, scale=scale, status=st)
+    if bias is not None:          # a table by distance [distances, n_q]; the tcgen05 kernel reads its transpose
+        common["dist_bias"] = bias.float().contiguous().to(DEV)
     if tiles:
-        o.attention_prefill(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), force=prefill, **common)
+        more = {"dist_bias_by_head": bias.float().t().contiguous().to(DEV)} if bias is not None else {}
+        o.attention_prefill(work=dev(np.array(tiles).reshape(-1)), n_work=len(tiles), force=prefill, **more, **common)
     if len(dec):
         splits = decode_splits(kv_lens[dec], window)
         ss = np.zeros(len(dec) + 1, np.int32)
@@ -307,7 +313,8 @@ def run_attention(dtype, n_q, n_kv, hd, page, seqs, window=0, scale=None, boost=
     for s, (kv, ql) in enumerate(seqs):
         for i in range(ql):
             t = q_start[s] + i
-            want[t] = ref_attention(q[t].double().view(n_q, hd), keys[s], vals[s], kv - ql + i, n_kv, window, scale)
+            want[t] = ref_attention(q[t].double().view(n_q, hd), keys[s], vals[s], kv - ql + i, n_kv, window, scale,
+                                    None if bias is None else bias.double())
     return out.view(T, n_q, hd), want
 
 
@@ -484,6 +491,23 @@ def test_prefill_tcgen05_kernel(n_q, n_kv, hd, page, window):
     torch.manual_seed(6)
     fast, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, prefill="tc")
     close(fast, want, 1.5e-2)
+
+
+@pytest.mark.parametrize("kernel", ["tc", "mma", "simt"])
+@pytest.mark.parametrize("n_q,n_kv,hd,page", [(8, 2, 128, 16), (6, 2, 64, 8), (16, 1, 64, 16)])
+@pytest.mark.parametrize("window,distances", [(0, 90), (70, 70), (200, 33)])
+def test_bias_tabulated_by_distance_in_every_attention_kernel(kernel, n_q, n_kv, hd, page, window, distances):
+    """Large random entries per (distance, head), the last row serving every longer distance: portions through the
+    named kernel, single queries through the tensor-core split kernel (the CUDA-core one with "simt")."""
+    seqs = [(37, 37), (300, 1), (65, 20), (128, 128), (129, 1), (200, 33), (256, 2), (700, 257), (1, 1), (513, 200), (1000, 1)]
+    torch.manual_seed(8)
+    bias = 2.0 * torch.randn(distances, n_q)
+    got, want = run_attention(torch.bfloat16, n_q, n_kv, hd, page, seqs, window=window, prefill=kernel,
+                              force_simt=kernel == "simt", bias=bias)
+    close(got, want, 1.5e-2)
+    if kernel == "simt":
+        got, want = run_attention(torch.float32, n_q, n_kv, hd, page, seqs, window=window, force_simt=True, bias=bias)
+        close(got, want, 3e-6)
 
 
 @pytest.mark.parametrize("prefill", ["tc", "mma", "simt"])
