@@ -1,7 +1,7 @@
 """rustingstrata_b200: a small, whole inference engine for one B200 (sm_100a).
 
 Everything between a request's token ids and its next token for the Qwen3 dense
-decoder (and, from further parts of the same engine, the Lokinex decoder), with the capabilities of RustingStudio/RustingStrata's engine: typed
+decoder (and, from further parts of the same engine, the Lokinex and Tabedra decoders), with the capabilities of RustingStudio/RustingStrata's engine: typed
 configuration and architecture registry, safetensors weights, layers assembled from
 parts, a paged key/value cache, one step function for mixed prefill/decode batches, a
 continuous-batching scheduler, greedy and temperature sampling, and hand-written CUDA
