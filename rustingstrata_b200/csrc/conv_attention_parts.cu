@@ -95,23 +95,58 @@ __device__ __forceinline__ void store_run(void* p, int dt, size_t i, bool vec, i
 // A warp per (token, head); a lane owns VEC neighbouring channels of the head (32 * VEC >= the padded head size).  The
 // warps of a CTA take neighbouring tokens of one head: the rows that the taps of one token read are the rows its
 // neighbours read, so all but the first read of a row is served by the SM's own cache.
+// which channels of a projected row head item `item` covers, and what it is (0 a query head, 1 a key head, 2 a value head)
+__device__ __forceinline__ void item_span(const ConvKvParams& p, int item, int& base, int& width, int& kind) {
+    if (item < p.n_q) { kind = 0; base = item * p.dk; width = p.dk; }
+    else if (item < p.n_q + p.n_kv) { kind = 1; base = p.n_q * p.dk + (item - p.n_q) * p.dk; width = p.dk; }
+    else { kind = 2; base = (p.n_q + p.n_kv) * p.dk + (item - p.n_q - p.n_kv) * p.dv; width = p.dv; }
+}
+
+// the warp's convolved head of token t (acc: this lane's VEC channels, zero beyond the head): unit norm, then to the
+// query rows or the token's cache page, padding included
+template <int VEC>
+__device__ __forceinline__ void norm_and_store(const ConvKvParams& p, int vec_ok, int t, int s, int item, int kind, int width,
+                                               int lane, float* acc) {
+    const int d0 = lane * VEC;
+    float r = 1.0f;
+    if (p.unit_norm && kind != 2) {
+        float ss = 0.f;
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) ss = fmaf(acc[q], acc[q], ss);
+        ss = warp_sum(ss);
+        r = 1.0f / sqrtf(ss / (float)width + p.eps);
+    }
+    void* dst; size_t o;
+    if (kind == 0) {
+        dst = p.q_out; o = (size_t)t * p.q_stride + (size_t)item * p.hdp;
+    } else {
+        const int pos = p.positions[(size_t)t * p.pos_stride];
+        const int page = p.block_table[(size_t)s * p.table_stride + pos / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+            if (lane == 0) atomicOr(p.status, RS_STATUS_BAD_PAGE);
+            return;
+        }
+        const int g = kind == 1 ? item - p.n_q : item - p.n_q - p.n_kv;
+        dst = p.cache;
+        o = (size_t)page * p.page_stride + ((size_t)g * p.page_size + pos % p.page_size) * p.hdp + (kind == 2 ? p.v_offset : 0);
+    }
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] *= r;
+    const int n_out = min(max(p.hdp - d0, 0), VEC);    // the padding behind the head is written too (zeros)
+    if (n_out > 0) store_run<VEC>(dst, p.dt, o + d0, vec_ok && n_out == VEC, n_out, acc);
+}
+
+// One (token, head) by a warp; a lane owns VEC neighbouring channels of the head (32 * VEC >= the padded head size).
 // FAST: bfloat16 rows and weights with every run aligned (vec_ok): loads without run-time type or alignment branches, and
 // for a token whose taps all read rows of this step, a loop the compiler can unroll with its loads issued together
 // (one tap's load after the other's arithmetic made the kernel wait out the memory latency once per tap).
 template <int VEC, bool FAST>
-__global__ void __launch_bounds__(256) conv_norm_kv_write_kernel(const ConvKvParams p, const int vec_ok) {
-    const int lane = threadIdx.x & 31;
-    const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
-    const unsigned wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // the launcher keeps tokens * items below 2^31
-    if (wid >= (unsigned)p.n_tokens * (unsigned)items) return;
-    const int item = (int)(wid / (unsigned)p.n_tokens), t = (int)(wid - (unsigned)item * (unsigned)p.n_tokens);
+__device__ __forceinline__ void conv_one(const ConvKvParams& p, int vec_ok, int t, int item, int lane) {
     const int s = p.seq_of_token[t];
     const int row0 = p.q_start[s], li = t - row0;
     const float* tail = p.tail + (size_t)p.slots[s] * p.tail_stride;
-    int base, width, kind;                             // kind 0 q, 1 k, 2 v
-    if (item < p.n_q) { kind = 0; base = item * p.dk; width = p.dk; }
-    else if (item < p.n_q + p.n_kv) { kind = 1; base = p.n_q * p.dk + (item - p.n_q) * p.dk; width = p.dk; }
-    else { kind = 2; base = (p.n_q + p.n_kv) * p.dk + (item - p.n_q - p.n_kv) * p.dv; width = p.dv; }
+    int base, width, kind;
+    item_span(p, item, base, width, kind);
     const int d0 = lane * VEC;
     const int n = min(max(width - d0, 0), VEC);        // this lane's channels inside the head
     const bool vec = vec_ok && n == VEC;
@@ -144,32 +179,69 @@ __global__ void __launch_bounds__(256) conv_norm_kv_write_kernel(const ConvKvPar
             }
         }
     }
-    float r = 1.0f;
-    if (p.unit_norm && kind != 2) {
-        float ss = 0.f;
-#pragma unroll
-        for (int q = 0; q < VEC; ++q) ss = fmaf(acc[q], acc[q], ss);       // channels beyond the head hold zero
-        ss = warp_sum(ss);
-        r = 1.0f / sqrtf(ss / (float)width + p.eps);
+    norm_and_store<VEC>(p, vec_ok, t, s, item, kind, width, lane, acc);
+}
+
+// The warps of a CTA take neighbouring tokens of one head.
+template <int VEC, bool FAST>
+__global__ void __launch_bounds__(256) conv_norm_kv_write_kernel(const ConvKvParams p, const int vec_ok) {
+    const int lane = threadIdx.x & 31;
+    const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
+    const unsigned wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // the launcher keeps tokens * items below 2^31
+    if (wid >= (unsigned)p.n_tokens * (unsigned)items) return;
+    const int item = (int)(wid / (unsigned)p.n_tokens), t = (int)(wid - (unsigned)item * (unsigned)p.n_tokens);
+    conv_one<VEC, FAST>(p, vec_ok, t, item, lane);
+}
+
+// TPW neighbouring tokens of one head by a warp, for TAPS known at compile time and the FAST conditions: when the
+// tokens belong to one sequence and none of their taps reaches before this step's rows, the warp loads the
+// TAPS - 1 + TPW rows they read once, the head's weights once and the index arrays once; a tap's products are added
+// in the order of the one-token form, so both forms give the same bits.  Any other group of tokens goes token by token.
+template <int VEC, int TAPS, int TPW>
+__global__ void __launch_bounds__(256) conv_norm_kv_write_multi_kernel(const ConvKvParams p) {
+    const int lane = threadIdx.x & 31;
+    const int items = p.n_q + (p.write_kv ? 2 * p.n_kv : 0);
+    const unsigned groups = (unsigned)(p.n_tokens + TPW - 1) / TPW;
+    const unsigned wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= groups * (unsigned)items) return;
+    const int item = (int)(wid / groups), t0 = (int)(wid - (unsigned)item * groups) * TPW;
+    const int nt = min(TPW, p.n_tokens - t0);
+    const int s = p.seq_of_token[t0];
+    const bool together = nt == TPW && p.seq_of_token[t0 + TPW - 1] == s && t0 - p.q_start[s] >= TAPS - 1;
+    if (!together) {
+        for (int tt = 0; tt < nt; ++tt) conv_one<VEC, true>(p, 1, t0 + tt, item, lane);
+        return;
     }
-    void* dst; size_t o;
-    if (kind == 0) {
-        dst = p.q_out; o = (size_t)t * p.q_stride + (size_t)item * p.hdp;
-    } else {
-        const int pos = p.positions[(size_t)t * p.pos_stride];
-        const int page = p.block_table[(size_t)s * p.table_stride + pos / p.page_size];
-        if (page < 0 || page >= p.num_pages) {
-            if (lane == 0) atomicOr(p.status, RS_STATUS_BAD_PAGE);
-            return;
+    int base, width, kind;
+    item_span(p, item, base, width, kind);
+    const int d0 = lane * VEC;
+    float acc[TPW][VEC];
+#pragma unroll
+    for (int tt = 0; tt < TPW; ++tt)
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) acc[tt][q] = 0.f;
+    if (width - d0 >= VEC) {                            // runs are whole under the FAST conditions
+        const int c = base + d0;
+        float w[TAPS][VEC];
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) load_run<VEC>(p.w, RS_BF16, (size_t)j * p.C + c, true, VEC, w[j]);
+        const size_t r0 = (size_t)(t0 - (TAPS - 1)) * p.proj_stride + c;
+#pragma unroll
+        for (int r = 0; r < TAPS - 1 + TPW; ++r) {
+            float x[VEC];
+            load_run<VEC>(p.proj, RS_BF16, r0 + (size_t)r * p.proj_stride, true, VEC, x);
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                const int tt = r - j;                   // row r is tap j of token tt
+                if (tt >= 0 && tt < TPW) {
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) acc[tt][q] = fmaf(w[j][q], x[q], acc[tt][q]);
+                }
+            }
         }
-        const int g = kind == 1 ? item - p.n_q : item - p.n_q - p.n_kv;
-        dst = p.cache;
-        o = (size_t)page * p.page_stride + ((size_t)g * p.page_size + pos % p.page_size) * p.hdp + (kind == 2 ? p.v_offset : 0);
     }
 #pragma unroll
-    for (int q = 0; q < VEC; ++q) acc[q] *= r;
-    const int n_out = min(max(p.hdp - d0, 0), VEC);    // the padding behind the head is written too (zeros)
-    if (n_out > 0) store_run<VEC>(dst, p.dt, o + d0, vec_ok && n_out == VEC, n_out, acc);
+    for (int tt = 0; tt < TPW; ++tt) norm_and_store<VEC>(p, 1, t0 + tt, s, item, kind, width, lane, acc[tt]);
 }
 
 // tail[i] <- the projected row at local index q_len - (taps - 1) + i: a row of this step, or a row the tail held.
@@ -237,7 +309,23 @@ RS_EXPORT int rs_conv_norm_kv_write(const void* proj, int dt, long proj_stride, 
                         ((size_t)cache % (vec_n * es)) == 0 && ((size_t)tails % (vec_n * 4)) == 0 &&
                         ((size_t)w % (vec_n * (w_dt == RS_F32 ? 4 : 2))) == 0;
     const bool fast = vec_ok && dt == RS_BF16 && (taps <= 0 || w_dt == RS_BF16);
-    if (fast) {
+    constexpr int TPW = 4;
+    // several tokens a warp where the step is mostly portions; a step of single tokens keeps a warp per token
+    if (fast && taps >= 2 && taps <= 4 && n_tokens >= 2 * TPW * n_seqs) {
+        const long groups = (n_tokens + TPW - 1) / TPW;
+        const unsigned mblocks = (unsigned)((groups * (n_q + (write_kv ? 2 * n_kv : 0)) + 7) / 8);
+#define RS_CONV_MULTI(V)                                                                                   \
+        do {                                                                                               \
+            if (taps == 2) conv_norm_kv_write_multi_kernel<V, 2, TPW><<<mblocks, 256, 0, s>>>(p);          \
+            else if (taps == 3) conv_norm_kv_write_multi_kernel<V, 3, TPW><<<mblocks, 256, 0, s>>>(p);     \
+            else conv_norm_kv_write_multi_kernel<V, 4, TPW><<<mblocks, 256, 0, s>>>(p);                    \
+        } while (0)
+        if (vec_n == 1) RS_CONV_MULTI(1);
+        else if (vec_n == 2) RS_CONV_MULTI(2);
+        else if (vec_n == 4) RS_CONV_MULTI(4);
+        else RS_CONV_MULTI(8);
+#undef RS_CONV_MULTI
+    } else if (fast) {
         if (vec_n == 1) conv_norm_kv_write_kernel<1, true><<<blocks, 256, 0, s>>>(p, vec_ok);
         else if (vec_n == 2) conv_norm_kv_write_kernel<2, true><<<blocks, 256, 0, s>>>(p, vec_ok);
         else if (vec_n == 4) conv_norm_kv_write_kernel<4, true><<<blocks, 256, 0, s>>>(p, vec_ok);
